@@ -58,13 +58,66 @@ class ReaLMoEConfig:
     input_jitter_eps: float = 0.0
     use_grouped_gemm: bool = True
     expert_parallel: bool = False  # partition experts over the TP group (all-to-all dispatch); reference: not available
+    # ---- routing variants of heterogeneous stacks (B200 addition).  routing_type "softmax_all": scores = softmax over ALL router
+    # outputs; the top_k largest of (scores + `mlp.router.correction`, when `score_correction`) are chosen; the weights are the
+    # chosen experts' scores, divided by their sum only with `renormalize`.
+    score_correction: bool = False
+    renormalize: bool = True
+    identity_experts: int = 0      # the router has num_experts + identity_experts outputs; the last ones pass their input through
+    shared_ff: Optional[int] = None  # a shared expert of this width runs for every token, times sigmoid(w_sg . x) (one number per token)
+
+    @property
+    def n_router_outputs(self) -> int:
+        return self.num_experts + self.identity_experts
+
+
+@dataclasses.dataclass
+class RotaryConfig:
+    """Rotation of the pairs (2i, 2i + 1) (`interleaved`) of the first `dims` dimensions of a vector by the angle pos * f_i,
+    f_i = base^(-2i / dims).  With `factor` (YaRN rescaling of a model trained on `original` positions): with
+    dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and
+    sin are multiplied by 0.1 ln(factor) + 1."""
+    dims: int
+    base: float = 10000.0
+    interleaved: bool = True
+    factor: Optional[float] = None
+    original: int = 0
+    fast: float = 32.0
+    slow: float = 1.0
+
+    def frequencies(self) -> Tuple[List[float], float]:
+        """(f_i for i < dims / 2 in double precision, the factor on cos and sin)."""
+        import math
+        n = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(n)]
+        if self.factor is None:
+            return f, 1.0
+
+        def dim_of(turns: float) -> float:
+            return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+        lo = max(math.floor(dim_of(self.fast)), 0)
+        hi = min(math.ceil(dim_of(self.slow)), self.dims - 1)
+        out = []
+        for i in range(n):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f[i] / self.factor * ramp + f[i] * (1.0 - ramp))
+        return out, 0.1 * math.log(self.factor) + 1.0
 
 
 @dataclasses.dataclass
 class LatentAttentionConfig:
-    """Attention whose keys and values are up-projections of one shared low-rank latent per token (only the latent is cached),
-    without positional rotation.  `window`: a query at position i sees positions (i - window, i]; None = the whole prefix.
-    `kv_from`: 0-based index of an EARLIER block whose cached latent this block reads instead of projecting its own."""
+    """Attention whose keys and values are up-projections of one shared low-rank latent per token (only the latent is cached).
+    `window`: a query at position i sees positions (i - window, i]; None = the whole prefix.
+    `kv_from`: 0-based index of an EARLIER block whose cached latent this block reads instead of projecting its own.
+    Further mechanisms, each a switch or a size:
+      * `rot_dim` > 0: every head's query / key gets `rot_dim` more dimensions that carry the position (`rotary`); the key part is
+        ONE vector per token shared by all heads, the last `rot_dim` outputs of the down-projection, cached beside the latent
+        (a cache row is [latent | rotated key part]).  `qk_dim` counts the unrotated dimensions only; `scale` multiplies the
+        whole score;
+      * `q_rank`: queries are the up-projection of an RMS-normalised latent of this rank (None: one projection);
+      * `sink`: a learned per-head logit in the softmax denominator (no key, no value);
+      * `out_gate`: the concatenated heads are multiplied element by element by sigmoid(W_g x), x the mixer's input."""
     n_heads: int
     qk_dim: int
     v_dim: int
@@ -72,6 +125,29 @@ class LatentAttentionConfig:
     scale: float
     window: Optional[int] = None
     kv_from: Optional[int] = None
+    rot_dim: int = 0
+    rotary: Optional[RotaryConfig] = None
+    q_rank: Optional[int] = None
+    sink: bool = False
+    out_gate: bool = False
+
+    def __post_init__(self):
+        if isinstance(self.rotary, dict):
+            self.rotary = RotaryConfig(**self.rotary)
+        if self.rot_dim:
+            if self.rotary is None or self.rotary.dims != self.rot_dim or self.rot_dim % 2 or not self.rotary.interleaved:
+                raise ValueError("rot_dim > 0 needs an interleaved `rotary` over exactly rot_dim (even) dimensions")
+            if self.kv_from is not None or self.window is not None:
+                raise ValueError("the rotated form has its own latent and no window")
+
+    @property
+    def rotated(self) -> bool:
+        """The mixer of `models.hetero_block._latent_rope_*` (any of rot_dim / q_rank / sink / out_gate set)."""
+        return bool(self.rot_dim or self.q_rank or self.sink or self.out_gate)
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_rank + self.rot_dim
 
 
 @dataclasses.dataclass
@@ -85,7 +161,11 @@ class WindowAttentionConfig:
       * `head_temp`: a learned per-head factor on the scaled score;
       * `slope_base` b: the score loses slope_h * (i - j), slope_h = 2^(-b (h + 1) / n_heads) (None: no distance term);
       * `sink`: a learned per-head logit added to the softmax denominator as exp(sink_h): a key-less, value-less entry;
-      * `out_gate`: head h's output is multiplied by sigmoid(w_g . x)_h, x being the mixer's input."""
+      * `out_gate`: head h's output is multiplied by sigmoid(w_g . x)_h, x being the mixer's input;
+      * `qk_norm`: every query / key head is RMS-normalised over qk_dim with a weight (one for queries, one for keys);
+      * `n_maps` = 2: differential attention.  Queries and keys have two maps per head ([map 1 | map 2], 2 qk_dim wide), each a
+        softmax attention of its own over the same values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + `diff` (learned vectors
+        of size qk_dim, one number per layer) head h's output is o = a1 - lambda a2, then o / sqrt(mean(o^2) + eps) * (1 - diff)."""
     n_heads: int
     n_kv_heads: int
     qk_dim: int
@@ -99,10 +179,17 @@ class WindowAttentionConfig:
     slope_base: Optional[float] = 8.0
     sink: bool = True
     out_gate: bool = True
+    qk_norm: bool = False
+    n_maps: int = 1
+    diff: float = 0.0
 
     def __post_init__(self):
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.n_maps not in (1, 2):
+            raise ValueError("n_maps: 1 (plain) or 2 (differential)")
+        if self.n_maps == 2 and (self.out_gate or self.sink or self.head_temp or self.slope_base is not None or self.value_norm or self.qkv_bias):
+            raise ValueError("differential attention combines with qk_norm and the window only")
         if self.window is None:
             self.keep_first = 0
         elif self.window < 1 or self.keep_first < 0:
@@ -140,13 +227,28 @@ class DeltaRuleConfig:
 
 
 @dataclasses.dataclass
+class MLSTMConfig:
+    """Matrix-memory LSTM mixer: per head a matrix state S [qk_dim, v_dim], a normaliser n [qk_dim] and a running maximum m (from
+    0) of the log gates, all fp32.  With i = cap tanh((w_i . x + b_i) / cap), f = logsigmoid(cap tanh((w_f . x + b_f) / cap)):
+    m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k;  o = S^T q / (max(|n . q|, exp(-m')) + 1e-6),
+    q scaled by qk_dim^(-1/2).  Each head's o is divided by its root mean square, the concatenation multiplied by a weight and by
+    sigmoid(W_g x)."""
+    n_heads: int
+    qk_dim: int
+    v_dim: int
+    gate_cap: float = 15.0
+
+
+@dataclasses.dataclass
 class LoopConfig:
     """Blocks start .. stop - 1 (0-based) run `times` times in a row with the same weights, every pass with a cache / state of its
-    own.  With `inject`, each pass first mixes the embedding output x0 back in: x <- W_in [x; x0], W_in [hidden, 2 hidden]."""
+    own.  With `inject`, the embedding output x0 is mixed back in at the start of a pass: mode "linear": every pass,
+    x <- W_in [x; x0], W_in [hidden, 2 hidden]; mode "add": every pass but the first, x <- x + x0."""
     start: int
     stop: int
     times: int
     inject: bool = True
+    inject_mode: str = "linear"    # linear | add
 
 
 @dataclasses.dataclass
@@ -154,22 +256,25 @@ class BlockMLPConfig:
     """Feed-forward of one block of a heterogeneous stack.  kind `clamped_glu`: y = g * sigmoid(alpha g) * (u + 1) with
     g = min(gate, limit), u = clamp(up, -limit, limit); kind `moe`: `moe.num_experts` SiLU-gated experts of width `ff`, the
     `moe.top_k` largest router logits (with a router bias) are chosen and weighted by the softmax over the chosen logits;
-    kind `relu2`: down(relu(up(x))^2), no gate."""
-    kind: str                      # clamped_glu | moe | relu2
+    kind `relu2`: down(relu(up(x))^2), no gate; kind `glu`: down(act(gate(x)) * up(x)) with `act` silu or gelu_tanh.  The experts
+    of kind `moe` are SiLU-gated units of width `ff`; routing variants are fields of `moe`."""
+    kind: str                      # clamped_glu | moe | relu2 | glu
     ff: int
     limit: float = 0.0
     alpha: float = 1.702
     moe: Optional[ReaLMoEConfig] = None
+    act: str = "silu"
 
 
 @dataclasses.dataclass
 class BlockConfig:
     """One entry of `ReaLModelConfig.blocks` (a stack whose blocks differ from each other)."""
-    mixer: str                     # latent_attention | window_attention | delta
+    mixer: str                     # latent_attention | window_attention | delta | mlstm
     attn: Optional[LatentAttentionConfig] = None
     mlp: Optional[BlockMLPConfig] = None   # None: the block has no feed-forward sublayer
     wattn: Optional[WindowAttentionConfig] = None
     delta: Optional[DeltaRuleConfig] = None
+    mlstm: Optional[MLSTMConfig] = None
 
     def __post_init__(self):
         if isinstance(self.attn, dict):
@@ -178,7 +283,9 @@ class BlockConfig:
             self.wattn = WindowAttentionConfig(**self.wattn)
         if isinstance(self.delta, dict):
             self.delta = DeltaRuleConfig(**self.delta)
-        want = {"latent_attention": self.attn, "window_attention": self.wattn, "delta": self.delta}
+        if isinstance(self.mlstm, dict):
+            self.mlstm = MLSTMConfig(**self.mlstm)
+        want = {"latent_attention": self.attn, "window_attention": self.wattn, "delta": self.delta, "mlstm": self.mlstm}
         if self.mixer not in want:
             raise ValueError(f"unknown mixer `{self.mixer}`")
         if want[self.mixer] is None:
@@ -243,8 +350,8 @@ class ReaLModelConfig:
         if lp is None:
             return [(i, False) for i in range(1, L + 1)]
         runs = [(i + 1, False) for i in range(lp.start)]
-        for _ in range(lp.times):
-            runs += [(i + 1, i == lp.start) for i in range(lp.start, lp.stop)]
+        for p in range(lp.times):
+            runs += [(i + 1, i == lp.start and (p > 0 or lp.inject_mode == "linear")) for i in range(lp.start, lp.stop)]
         return runs + [(i + 1, False) for i in range(lp.stop, L)]
 
     def __post_init__(self):
@@ -255,6 +362,8 @@ class ReaLModelConfig:
                 raise ValueError("`loop` needs a heterogeneous stack (`blocks`)")
             if not (0 <= self.loop.start < self.loop.stop <= self.n_layers and self.loop.times >= 1):
                 raise ValueError("loop: 0 <= start < stop <= n_layers and times >= 1 expected")
+            if self.loop.inject_mode not in ("linear", "add"):
+                raise ValueError("loop.inject_mode: linear | add")
         if self.is_critic and self.tied_embedding:
             raise ValueError("a critic cannot tie its embedding and output weights")
         if self.blocks is not None:
@@ -264,6 +373,8 @@ class ReaLModelConfig:
             for i, b in enumerate(self.blocks):
                 if b.mixer != "latent_attention":
                     continue
+                if b.attn.rotated and (self.norm_groups != 1 or self.sandwich_norm or self.conv_taps):
+                    raise ValueError("rotated latent attention lives in plain pre-norm stacks")
                 src = b.attn.kv_from
                 if src is not None and not (0 <= src < i and self.blocks[src].attn.kv_from is None
                                             and self.blocks[src].attn.kv_rank == b.attn.kv_rank):
@@ -283,12 +394,24 @@ class ReaLModelConfig:
                 if b.mixer == "window_attention":
                     a = b.wattn
                     qkv = a.n_heads * a.qk_dim + a.n_kv_heads * (a.qk_dim + a.v_dim)
+                    qkv += (a.n_maps - 1) * (a.n_heads + a.n_kv_heads) * a.qk_dim
                     n += h * (qkv + (a.n_heads if a.out_gate else 0)) + (qkv if a.qkv_bias else 0) + a.n_heads * a.v_dim * h
                     n += a.n_heads * (int(a.head_temp) + int(a.sink)) + norms * h
+                    n += (2 * a.qk_dim if a.qk_norm else 0) + (4 * a.qk_dim if a.n_maps == 2 else 0)
                 elif b.mixer == "delta":
                     a = b.delta
                     n += h * (2 * a.n_kv_heads * a.qk_dim + 2 * a.n_heads * a.v_dim + 2 * a.n_heads) + a.n_heads * a.v_dim * h
                     n += a.conv_channels * a.conv_taps + 2 * a.n_heads + a.v_dim + norms * h
+                elif b.mixer == "mlstm":
+                    a = b.mlstm
+                    n += h * (2 * a.n_heads * a.qk_dim + 2 * a.n_heads * a.v_dim + 2 * a.n_heads) + 2 * a.n_heads
+                    n += a.n_heads * a.v_dim * (h + 1) + norms * h
+                elif b.attn.rotated:
+                    a = b.attn
+                    dq = a.qk_dim + a.rot_dim
+                    n += (h * a.q_rank + a.q_rank + a.q_rank * a.n_heads * dq) if a.q_rank else h * a.n_heads * dq
+                    n += h * a.cache_width + a.kv_rank + a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h
+                    n += (a.n_heads if a.sink else 0) + (h * a.n_heads * a.v_dim if a.out_gate else 0) + norms * h
                 else:
                     a = b.attn
                     n += h * a.n_heads * a.qk_dim + (h * a.kv_rank + a.kv_rank if a.kv_from is None else 0)
@@ -296,8 +419,15 @@ class ReaLModelConfig:
                 if b.mlp is not None:
                     e = b.mlp.moe.num_experts if b.mlp.kind == "moe" else 1
                     mats = 2 if b.mlp.kind == "relu2" else 3
-                    n += e * mats * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + norms * h
-            if self.loop is not None and self.loop.inject:
+                    n += e * mats * h * b.mlp.ff + norms * h
+                    if b.mlp.kind == "moe":
+                        mo = b.mlp.moe
+                        if mo.routing_type == "softmax_all":
+                            n += mo.n_router_outputs * (h + (1 if mo.score_correction else 0))
+                            n += (3 * h * mo.shared_ff + h) if mo.shared_ff else 0
+                        else:
+                            n += e * (h + 1)
+            if self.loop is not None and self.loop.inject and self.loop.inject_mode == "linear":
                 n += 2 * h * h
             return n
         qkv = h * self.head_dim * (self.n_q_heads + 2 * self.n_kv_heads)

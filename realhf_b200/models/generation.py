@@ -126,8 +126,18 @@ class DecodeState:
                 if b.mixer == "window_attention":
                     w = b.wattn
                     rows = w.cache_rows(S)
-                    self.k.append(torch.zeros(B, w.n_kv_heads, rows, w.qk_dim, dtype=dt, device=dev))
+                    self.k.append(torch.zeros(B, w.n_kv_heads * w.n_maps, rows, w.qk_dim, dtype=dt, device=dev))   # every map's keys
                     self.v.append(torch.zeros(B, w.n_kv_heads, rows, w.v_dim, dtype=dt, device=dev))
+                    continue
+                if b.mixer == "mlstm":
+                    ml = b.mlstm
+                    self.k.append(torch.zeros(B, ml.n_heads, ml.qk_dim, ml.v_dim + 1, dtype=torch.float32, device=dev))   # S | n
+                    self.v.append(torch.zeros(B, ml.n_heads, dtype=torch.float32, device=dev))                          # running maximum
+                    self.zeroed += [(self.k[-1], 0), (self.v[-1], 0)]
+                    continue
+                if b.mixer == "latent_attention" and b.attn.rotated:
+                    self.k.append(torch.zeros(B, S, b.attn.cache_width, dtype=dt, device=dev))
+                    self.v.append(torch.zeros(B, 0, dtype=torch.float32, device=dev))
                     continue
                 if b.mixer == "delta":
                     d = b.delta

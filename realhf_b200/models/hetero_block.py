@@ -12,7 +12,11 @@ per run (`state.k[r]`, `state.v[r]`), by mixer:
   * window attention: `k[r]` keys [n_slots, G, rows, d], `v[r]` normalised values [n_slots, G, rows, dv] (model dtype); position p
     in row p below `keep_first`, else in a ring of the remaining rows (`WindowAttentionConfig.cache_rows`);
   * delta rule: `k[r]` the matrix states [n_slots, H, d, dv] fp32, `v[r]` the last taps - 1 projection outputs
-    [n_slots, taps - 1, C] fp32.
+    [n_slots, taps - 1, C] fp32;
+  * differential window attention (`n_maps` = 2): `k[r]` [n_slots, 2G, rows, d] (both maps' keys), `v[r]` [n_slots, G, rows, dv];
+  * rotated latent attention: `k[r]` the ring [n_slots, R, kv_rank + rot_dim] of rows [latent | rotated key part], `v[r]` empty;
+  * matrix-memory LSTM: `k[r]` the states with the normaliser as last column [n_slots, H, d, dv + 1] fp32, `v[r]` the running
+    maxima [n_slots, H] fp32.
 
 Inference only (no autograd through these kernels) and not tensor-parallel.  A stack with a loop runs on one pipeline stage.
 """
@@ -66,6 +70,8 @@ def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
         return moe.moe_forward(model, i, h, mcfg.moe)
     if mcfg.kind == "relu2":
         return OF.linear(OF.relu2_linear(h, p[f"{i}.mlp.up.weight"]), p[f"{i}.mlp.down.weight"])
+    if mcfg.kind == "glu":
+        return OF.linear(OF.gated_linear(h, p[f"{i}.mlp.gate_up.weight"], mcfg.act), p[f"{i}.mlp.down.weight"])
     a = OF.clamped_gated_linear(h, p[f"{i}.mlp.gate_up.weight"], mcfg.limit, mcfg.alpha)
     return OF.linear(a, p[f"{i}.mlp.down.weight"])
 
@@ -75,6 +81,11 @@ def _window_attention_packed(model, i: int, li: int, h: torch.Tensor, meta: Pack
     a = c.blocks[i - 1].wattn
     keep = meta.k is not None
     qkvg = OF.linear(h, p[f"{i}.attn.qkvg.weight"], p.get(f"{i}.attn.qkvg.bias"))
+    if a.n_maps == 2:
+        o = attn_ops.diff_window_attention(qkvg, a, p[f"{i}.attn.q_norm.weight"], p[f"{i}.attn.k_norm.weight"], p[f"{i}.attn.lambda.weight"],
+                                           c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None, meta.tok_slot,
+                                           meta.pos, meta.remain, meta.cu_seqlens, meta.max_seqlen)
+        return OF.linear(o, p[f"{i}.attn.o.weight"])
     v_n = attn_ops.value_norm_store(qkvg, a, c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None,
                                     meta.tok_slot, meta.pos, meta.remain)
     o = attn_ops.sink_window_attention(qkvg, v_n, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), meta.pos,
@@ -86,6 +97,10 @@ def _window_attention_decode(model, i: int, li: int, h: torch.Tensor, k_caches, 
     c, p = model.config, model.p
     a = c.blocks[i - 1].wattn
     qkvg = OF.linear(h, p[f"{i}.attn.qkvg.weight"], p.get(f"{i}.attn.qkvg.bias"))
+    if a.n_maps == 2:
+        o = attn_ops.diff_window_decode_attention(qkvg, a, p[f"{i}.attn.q_norm.weight"], p[f"{i}.attn.k_norm.weight"], p[f"{i}.attn.lambda.weight"],
+                                                  c.layer_norm_epsilon, k_caches[li], v_caches[li], cache_lens, slots)
+        return OF.linear(o, p[f"{i}.attn.o.weight"])
     o = attn_ops.sink_window_decode_attention(qkvg, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), k_caches[li],
                                               v_caches[li], cache_lens, slots, c.layer_norm_epsilon)
     return OF.linear(o, p[f"{i}.attn.o.weight"])
@@ -118,8 +133,79 @@ def _delta_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, s
     return OF.linear(_delta_out(model, i, d, o, proj), p[f"{i}.attn.o.weight"])
 
 
+def _mlstm_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+    c, p = model.config, model.p
+    m = c.blocks[i - 1].mlstm
+    keep = meta.k is not None
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    o, mx = rec_ops.mlstm_scan(proj, p[f"{i}.attn.gate_bias.weight"], m, meta.cu_seqlens, meta.k[li] if keep else None,
+                               meta.v[li] if keep else None, meta.seq_slot if keep else None)
+    return OF.linear(_mlstm_out(model, i, m, o, mx, proj), p[f"{i}.attn.o.weight"])
+
+
+def _mlstm_out(model, i: int, m, o, mx, proj) -> torch.Tensor:
+    g0 = 2 * m.n_heads * m.qk_dim + m.n_heads * m.v_dim
+    return rec_ops.mlstm_out(o, mx, model.p[f"{i}.attn.o_norm.weight"], proj[:, g0:g0 + m.n_heads * m.v_dim], model.config.layer_norm_epsilon,
+                             model.dtype)
+
+
+def _mlstm_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, slots) -> torch.Tensor:
+    p = model.p
+    m = model.config.blocks[i - 1].mlstm
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    o, mx = rec_ops.mlstm_step(proj, p[f"{i}.attn.gate_bias.weight"], m, k_caches[li], v_caches[li], slots)
+    return OF.linear(_mlstm_out(model, i, m, o, mx, proj), p[f"{i}.attn.o.weight"])
+
+
+def _latent_rope_queries(model, i: int, a, proj: torch.Tensor, cq: Optional[torch.Tensor]) -> torch.Tensor:
+    """[rows, H (d + rot)] queries, not yet rotated: the up-projection of the normalised query latent, or a section of `proj`."""
+    if a.q_rank:
+        return OF.linear(cq, model.p[f"{i}.attn.uq.weight"])
+    q0 = a.cache_width + (a.n_heads * a.v_dim if a.out_gate else 0)
+    return proj[:, q0:q0 + a.n_heads * (a.qk_dim + a.rot_dim)]
+
+
+def _latent_rope_gate(a, o: torch.Tensor, proj: torch.Tensor) -> torch.Tensor:
+    if a.out_gate:
+        g0 = (a.q_rank or 0) + a.cache_width
+        attn_ops.sigmoid_gate_(o, proj[:, g0:g0 + a.n_heads * a.v_dim])
+    return o
+
+
+def _latent_rope_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+    c, p = model.config, model.p
+    a = c.blocks[i - 1].attn
+    keep = meta.k is not None
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    cq, lat = attn_ops.latent_rope_prepare(proj, a, p.get(f"{i}.attn.q_ln.weight"), p[f"{i}.attn.dkv_ln.weight"], c.layer_norm_epsilon, meta.pos,
+                                           meta.k[li] if keep else None, meta.tok_slot, meta.remain)
+    q = _latent_rope_queries(model, i, a, proj, cq)
+    kv = OF.linear(lat[:, : a.kv_rank], p[f"{i}.attn.ukv.weight"])
+    o = attn_ops.latent_rope_attention(q, kv, lat, a, p.get(f"{i}.attn.sink.weight"), meta.pos, meta.cu_seqlens, meta.max_seqlen)
+    return OF.linear(_latent_rope_gate(a, o, proj), p[f"{i}.attn.o.weight"])
+
+
+def _latent_rope_decode(model, i: int, li: int, h: torch.Tensor, k_caches, cache_lens, slots) -> torch.Tensor:
+    c, p = model.config, model.p
+    a = c.blocks[i - 1].attn
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    cq, _ = attn_ops.latent_rope_prepare(proj, a, p.get(f"{i}.attn.q_ln.weight"), p[f"{i}.attn.dkv_ln.weight"], c.layer_norm_epsilon, None,
+                                         k_caches[li], cache_lens=cache_lens, slots=slots, want_lat=False)
+    q = _latent_rope_queries(model, i, a, proj, cq)
+    o = attn_ops.latent_rope_decode_attention(q, a, p[f"{i}.attn.ukv.weight"], p.get(f"{i}.attn.sink.weight"), k_caches[li], cache_lens, slots)
+    return OF.linear(_latent_rope_gate(a, o, proj), p[f"{i}.attn.o.weight"])
+
+
+def norm_offset(c) -> float:
+    """What is added to a stored norm weight: 1 for weights stored around zero (`layer_norm_type` "gemma")."""
+    return 1.0 if c.layer_norm_type == "gemma" else 0.0
+
+
 def loop_inject(model, i: int, x: torch.Tensor, x0: torch.Tensor) -> torch.Tensor:
-    """Start of a pass of the loop: x <- W_in [x; x0] (x0 = the embedding output), back on the residual stream's dtype."""
+    """Start of a pass of the loop.  Mode "linear": x <- W_in [x; x0] (x0 = the embedding output), back on the residual stream's
+    dtype; mode "add": x <- x + x0 in place."""
+    if model.config.loop.inject_mode == "add":
+        return OF.residual_add_norm_(x, x0, None, 1, model.config.layer_norm_epsilon)
     cat = OF.concat_cast(x, x0, model.dtype)
     w = model.p[f"{i}.loop_in.weight"]
     return OF.linear_f32(cat, w) if x.dtype == torch.float32 else OF.linear(cat, w).to(x.dtype)
@@ -132,10 +218,10 @@ def plain_prenorm(c) -> bool:
 
 def first_norm(model, i: int, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
     """Input of block i's mixer in a plain pre-norm stack; a branch output still owed to the stream is added in the same kernel."""
-    w, eps = model.p[f"{i}.attn.ln.weight"], model.config.layer_norm_epsilon
+    w, eps, off = model.p[f"{i}.attn.ln.weight"], model.config.layer_norm_epsilon, norm_offset(model.config)
     if pending is not None:
-        return OF.add_rms_norm_(x, pending, w, eps, model.dtype)
-    return OF.sublayer_input(x, w, 1, eps, None, None, model.dtype)
+        return OF.add_rms_norm_(x, pending, w, eps, model.dtype, off)
+    return OF.sublayer_input(x, w, 1, eps, None, None, model.dtype, w_offset=off)
 
 
 def settle(model, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
@@ -158,10 +244,10 @@ def _finish_block(model, i: int, b, x: torch.Tensor, y: torch.Tensor, defer: boo
         OF.residual_add_norm_(x, y, post, G, eps)
         return None
     if post is None and G == 1:
-        h = OF.add_rms_norm_(x, y, p[f"{i}.mlp.ln.weight"], eps, model.dtype)
+        h = OF.add_rms_norm_(x, y, p[f"{i}.mlp.ln.weight"], eps, model.dtype, norm_offset(c))
     else:
         OF.residual_add_norm_(x, y, post, G, eps)
-        h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype)
+        h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype, w_offset=norm_offset(c))
     y2 = _mlp(model, i, h, b.mlp)
     post2 = p.get(f"{i}.mlp.ln_post.weight")
     if defer and post2 is None:
@@ -179,12 +265,13 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta, pend
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     keep = meta.k is not None
-    if b.mixer != "latent_attention":
+    if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G, eps,
-                                                                                       None, None, model.dtype)
-        y = _window_attention_packed(model, i, li, h, meta) if b.mixer == "window_attention" else _delta_packed(model, i, li, h, meta)
-        return x, _finish_block(model, i, b, x, y, defer)
+                                                                                       None, None, model.dtype, w_offset=norm_offset(c))
+        mixer = {"window_attention": _window_attention_packed, "delta": _delta_packed, "mlstm": _mlstm_packed,
+                 "latent_attention": _latent_rope_packed}[b.mixer]
+        return x, _finish_block(model, i, b, x, mixer(model, i, li, h, meta), defer)
     settle(model, x, pending)
     conv = meta.v[li] if keep and c.conv_taps else None
     h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"), meta.pos, model.dtype,
@@ -216,12 +303,17 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
-    if b.mixer != "latent_attention":
+    if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input_step(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G,
-                                                                                            eps, None, None, slots, model.dtype)
+                                                                                            eps, None, None, slots, model.dtype,
+                                                                                            w_offset=norm_offset(c))
         if b.mixer == "window_attention":
             y = _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
+        elif b.mixer == "mlstm":
+            y = _mlstm_decode(model, i, li, h, k_caches, v_caches, slots)
+        elif b.mixer == "latent_attention":
+            y = _latent_rope_decode(model, i, li, h, k_caches, cache_lens, slots)
         else:
             y = _delta_decode(model, i, li, h, k_caches, v_caches, slots)
         return x, _finish_block(model, i, b, x, y, defer)
@@ -245,8 +337,8 @@ def final_norm(model, x: torch.Tensor, pending: Optional[torch.Tensor] = None) -
     c = model.config
     w = model.p[f"{c.n_layers}.ln_f.weight"]
     if pending is not None and plain_prenorm(c):
-        return OF.add_rms_norm_(x, pending, w, c.layer_norm_epsilon, model.dtype)
-    return OF.sublayer_input(settle(model, x, pending), w, c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype)
+        return OF.add_rms_norm_(x, pending, w, c.layer_norm_epsilon, model.dtype, norm_offset(c))
+    return OF.sublayer_input(settle(model, x, pending), w, c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype, w_offset=norm_offset(c))
 
 
 def ring_rows(cfg, block: int, max_len: int) -> int:

@@ -42,8 +42,11 @@ def sinkhorn(cost: torch.Tensor, tol: float = 1e-4, max_iter: int = 100) -> torc
     return d1 * cost * d0.unsqueeze(1)
 
 
-def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """h [T,H] -> (probs [T,k] fp32 normalised over the chosen experts, expert ids [T,k]).  Logits (+ `bias`) are fp32."""
+def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: Optional[torch.Tensor] = None,
+          correction: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """h [T,H] -> (probs [T,k] fp32 normalised over the chosen experts, expert ids [T,k]).  Logits (+ `bias`) are fp32.
+    routing_type "softmax_all": the scores are the softmax over all router outputs, `correction` is added to them for the
+    choice only, and the weights are the chosen scores themselves (divided by their sum only with `renormalize`)."""
     if training and mcfg.input_jitter_eps > 0:
         h = h * torch.empty_like(h).uniform_(1 - mcfg.input_jitter_eps, 1 + mcfg.input_jitter_eps)
     logits = F.linear(h.float(), w_router.float(), bias.float() if bias is not None else None)
@@ -54,6 +57,11 @@ def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: O
             _, idx = torch.topk(sinkhorn(logits), mcfg.top_k, dim=-1)
         probs = torch.sigmoid(logits).gather(-1, idx) if mcfg.top_k == 1 else torch.softmax(logits, -1).gather(-1, idx)
         return probs, idx
+    if mcfg.routing_type == "softmax_all":
+        full = torch.softmax(logits, dim=-1)
+        idx = torch.topk(full + correction.float() if correction is not None else full, mcfg.top_k, dim=-1).indices
+        probs = full.gather(-1, idx)
+        return (probs / probs.sum(-1, keepdim=True) if mcfg.renormalize else probs), idx
     if mcfg.routing_type == "none":  # the k largest logits, weighted by the softmax over those k alone
         top, idx = torch.topk(logits, mcfg.top_k, dim=-1)
         return torch.softmax(top, dim=-1), idx
@@ -112,13 +120,14 @@ def _use_grouped_kernel(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.
 
 
 def grouped_mlp(x_sorted: torch.Tensor, counts: List[int], w_gate_up: torch.Tensor, w_down: torch.Tensor, act: str):
-    """Tokens sorted by expert; expert e owns rows [sum(counts[:e]), +counts[e]).  w_gate_up [E,2F,H], w_down [E,H,F]."""
+    """Tokens sorted by expert; expert e owns rows [sum(counts[:e]), +counts[e]).  w_gate_up [E,2F,H], w_down [E,H,F].  Counts beyond
+    the E weight slices belong to identity experts: their rows pass through."""
     outs, off = [], 0
     for e, n in enumerate(counts):
         if n == 0:
             continue
         xe = x_sorted[off: off + n]
-        outs.append(OF.linear(OF.gated_act(OF.linear(xe, w_gate_up[e]), act), w_down[e]))
+        outs.append(OF.linear(OF.gated_act(OF.linear(xe, w_gate_up[e]), act), w_down[e]) if e < w_gate_up.shape[0] else xe)
         off += n
     if not outs:
         return x_sorted.new_zeros(0, w_down.shape[1])
@@ -142,7 +151,11 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
     else:
         h = TP.copy_to_tp(h, ctx)
     T, H = h.shape
-    probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"))
+    probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"),
+                       model.p.get(f"{i}.mlp.router.correction"))
+    n_id = mcfg.identity_experts            # router outputs E .. E + n_id - 1: the expert's output is its input
+    if n_id or mcfg.shared_ff:
+        assert not ep and ctx.tp_size == 1 and mcfg.capacity_factor is None, "identity / shared experts: single-rank stacks"
     probs = _apply_capacity(probs, idx, E, mcfg)
     flat_e = idx.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
@@ -201,16 +214,21 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         # operands the grouped kernel does not take (fp32) inside a CUDA-graph capture, where the per-expert loop's host read of
         # the counts is illegal: every expert runs on every row (decode batches are small) and the routing weight, zero for
         # the experts a row did not choose, selects; summed in expert order
-        gate = torch.zeros(T, E, dtype=torch.float32, device=h.device).scatter_(1, idx, probs.float())
+        gate = torch.zeros(T, E + n_id, dtype=torch.float32, device=h.device).scatter_(1, idx, probs.float())
         out = torch.zeros(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
         for e in range(E):
             y = OF.linear(OF.gated_act(OF.linear(h, w_gu[e]), c.activation_function), w_dn[e])
             out += (y.float() * gate[:, e: e + 1]).to(out.dtype)
-        return out
+        if n_id:
+            out += (h.float() * gate[:, E:].sum(1, keepdim=True)).to(out.dtype)
+        return _add_shared(model, i, h, mcfg, out)
     if grouped:
-        y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E), w_gu, w_dn, c.activation_function)
+        # the device-side offsets end at expert E: rows of identity experts (sorted last) are not touched by the GEMMs and pass through
+        y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E + n_id)[:E], w_gu, w_dn, c.activation_function)
+        if n_id:
+            y_sorted = torch.where((flat_e[order] >= E).unsqueeze(-1), x_sorted, y_sorted)
     else:
-        counts = torch.bincount(flat_e, minlength=E).tolist()
+        counts = torch.bincount(flat_e, minlength=E + n_id).tolist()
         y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, c.activation_function)
     if c.fp32_residual:
         # fp32 combine in a fixed order (an atomic index_add_ would make the sum depend on the run): rows back to (token, choice)
@@ -221,4 +239,14 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         out = torch.zeros(T, H, dtype=y_sorted.dtype, device=h.device).index_add_(0, tok, y_sorted * w_sorted.to(y_sorted.dtype).unsqueeze(-1))
     if ctx.tp_size > 1:  # experts are F-sharded over TP: partial sums
         out = TP.reduce_scatter_to_sp(out, ctx) if sp else TP.reduce_from_tp(out, ctx)
-    return out
+    return _add_shared(model, i, h, mcfg, out)
+
+
+def _add_shared(model, i: int, h: torch.Tensor, mcfg, out: torch.Tensor) -> torch.Tensor:
+    """out += shared expert(h) * sigmoid(w_sg . h): an expert every token uses, scaled by one learned gate value per token (fp32)."""
+    if not mcfg.shared_ff:
+        return out
+    p = model.p
+    y = OF.linear(OF.gated_linear(h, p[f"{i}.mlp.shared.gate_up.weight"], model.config.activation_function), p[f"{i}.mlp.shared.down.weight"])
+    g = torch.sigmoid(F.linear(h.float(), p[f"{i}.mlp.shared.sg.weight"].float()))
+    return out + (y.float() * g).to(out.dtype)

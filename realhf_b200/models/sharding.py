@@ -102,8 +102,22 @@ def wattn_sections(w) -> Tuple[int, ...]:
     """Rows of the fused input projection of a window-attention block: [queries | keys | values | output-gate logits].  The gate
     section (one row per head) is padded to a multiple of 8 rows so that the fused tensor keeps 16-byte row groups; the padding
     rows are never read."""
-    sec = (w.n_heads * w.qk_dim, w.n_kv_heads * w.qk_dim, w.n_kv_heads * w.v_dim)
+    sec = (w.n_heads * w.n_maps * w.qk_dim, w.n_kv_heads * w.n_maps * w.qk_dim, w.n_kv_heads * w.v_dim)   # n_maps = 2: two score maps per head
     return sec + ((_pad8(w.n_heads),) if w.out_gate else ())
+
+
+def mlstm_sections(m) -> Tuple[int, ...]:
+    """Rows of the fused input projection of a matrix-memory LSTM block: [q | k | v | output gate | input gate, forget gate].  The
+    last section holds one row per head for the input gate, then one per head for the forget gate, padded to a multiple of 8."""
+    return (m.n_heads * m.qk_dim, m.n_heads * m.qk_dim, m.n_heads * m.v_dim, m.n_heads * m.v_dim, _pad8(2 * m.n_heads))
+
+
+def latent_rope_sections(a) -> Tuple[int, ...]:
+    """Rows of the fused input projection of a rotated latent-attention block: [query latent | latent, rotated key part | gate
+    logits | queries].  The first section exists with `q_rank`, the third with `out_gate`, the last without `q_rank`."""
+    dq = a.qk_dim + a.rot_dim
+    return (((a.q_rank,) if a.q_rank else ()) + (a.kv_rank + a.rot_dim,) + ((a.n_heads * a.v_dim,) if a.out_gate else ())
+            + (() if a.q_rank else (a.n_heads * dq,)))
 
 
 def delta_sections(d) -> Tuple[int, ...]:
@@ -125,9 +139,10 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
 
     def add(*args, **kw):
         out.append(P(*args, **kw))
-    if cfg.loop is not None and cfg.loop.inject and layer_idx == cfg.loop.start + 1:
+    if cfg.loop is not None and cfg.loop.inject and cfg.loop.inject_mode == "linear" and layer_idx == cfg.loop.start + 1:
         add("loop_in.weight", (H, 2 * H), None)
-    add("attn.ln.weight", (H,), None, init="ones")
+    norm_init = "zeros" if cfg.layer_norm_type == "gemma" else "ones"    # "gemma": the factor is 1 + weight
+    add("attn.ln.weight", (H,), None, init=norm_init)
     if cfg.conv_taps:
         add("attn.canon.weight", (H, cfg.conv_taps), None)
     if b.mixer == "window_attention":
@@ -140,7 +155,31 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
             add("attn.temp.weight", (w.n_heads,), None, init="ones")
         if w.sink:
             add("attn.sink.weight", (w.n_heads,), None, init="zeros")
+        if w.qk_norm:
+            add("attn.q_norm.weight", (w.qk_dim,), None, init="ones")
+            add("attn.k_norm.weight", (w.qk_dim,), None, init="ones")
+        if w.n_maps == 2:
+            add("attn.lambda.weight", (4, w.qk_dim), None)     # lq1, lk1, lq2, lk2
         add("attn.o.weight", (H, w.n_heads * w.v_dim), None)
+    elif b.mixer == "mlstm":
+        m = b.mlstm
+        sec = mlstm_sections(m)
+        add("attn.in.weight", (sum(sec), H), None, sec)
+        add("attn.gate_bias.weight", (2 * m.n_heads,), None, init="zeros")
+        add("attn.o_norm.weight", (m.n_heads * m.v_dim,), None, init="ones")
+        add("attn.o.weight", (H, m.n_heads * m.v_dim), None)
+    elif b.mixer == "latent_attention" and a.rotated:
+        sec = latent_rope_sections(a)
+        add("attn.in.weight", (sum(sec), H), None, sec)
+        if a.q_rank:
+            add("attn.q_ln.weight", (a.q_rank,), None, init="ones")
+            add("attn.uq.weight", (a.n_heads * (a.qk_dim + a.rot_dim), a.q_rank), None)
+        add("attn.dkv_ln.weight", (a.kv_rank,), None, init="ones")
+        kv_sec = (a.n_heads * a.qk_dim, a.n_heads * a.v_dim)
+        add("attn.ukv.weight", (sum(kv_sec), a.kv_rank), None, kv_sec)
+        if a.sink:
+            add("attn.sink.weight", (a.n_heads,), None, init="zeros")
+        add("attn.o.weight", (H, a.n_heads * a.v_dim), None)
     elif b.mixer == "delta":
         d = b.delta
         sec = delta_sections(d)
@@ -163,15 +202,25 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
         add("attn.ln_post.weight", (H,), None, init="ones")
     if b.mlp is not None:
         F = b.mlp.ff
-        add("mlp.ln.weight", (H,), None, init="ones")
+        add("mlp.ln.weight", (H,), None, init=norm_init)
         if cfg.conv_taps:
             add("mlp.canon.weight", (H, cfg.conv_taps), None)
         if b.mlp.kind == "moe":
-            E = b.mlp.moe.num_experts
-            add("mlp.router.weight", (E, H), None)
-            add("mlp.router.bias", (E,), None, init="zeros")
+            mo = b.mlp.moe
+            E = mo.num_experts
+            if mo.routing_type == "softmax_all":
+                add("mlp.router.weight", (mo.n_router_outputs, H), None)
+                if mo.score_correction:
+                    add("mlp.router.correction", (mo.n_router_outputs,), None, init="zeros")
+            else:
+                add("mlp.router.weight", (E, H), None)
+                add("mlp.router.bias", (E,), None, init="zeros")
             add("mlp.experts.gate_up.weight", (E, 2 * F, H), None)
             add("mlp.experts.down.weight", (E, H, F), None)
+            if mo.shared_ff:
+                add("mlp.shared.gate_up.weight", (2 * mo.shared_ff, H), None, (mo.shared_ff, mo.shared_ff))
+                add("mlp.shared.down.weight", (H, mo.shared_ff), None)
+                add("mlp.shared.sg.weight", (1, H), None)
         elif b.mlp.kind == "relu2":
             add("mlp.up.weight", (F, H), None)
             add("mlp.down.weight", (H, F), None)
@@ -181,7 +230,7 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
         if cfg.sandwich_norm:
             add("mlp.ln_post.weight", (H,), None, init="ones")
     if layer_idx == cfg.n_layers:
-        add("ln_f.weight", (H,), None, init="ones")
+        add("ln_f.weight", (H,), None, init=norm_init)
     return out
 
 

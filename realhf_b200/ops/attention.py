@@ -506,3 +506,279 @@ def sink_window_decode_attention(qkvg, a, temp, sink, k_cache, v_cache, cache_le
                                            a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate), bool(a.value_norm), eps)
         return out
     return sink_window_decode_attention_ref(qkvg, a, temp, sink, k_cache, v_cache, cache_lens, slots, eps)
+
+
+# ------------------------------------------------------------------------------------------------ differential window attention
+# (`WindowAttentionConfig` with n_maps = 2).  The projection row holds [q (H x 2 x d) | k (G x 2 x d) | v (G x dv)]; the query heads are
+# stored grouped by key head and map, (g, map, head within the group), so that the kernels see 2H query heads over 2G key heads with
+# the ordinary grouping, two consecutive key heads sharing a value head.  Caches: k [n_slots, 2G, rows, d], v [n_slots, G, rows, dv].
+
+
+def diff_lambda(w_lambda, diff: float):
+    """fp32 [1] on the weight's device: exp(lq1 . lk1) - exp(lq2 . lk2) + diff from the [4, d] parameter (lq1, lk1, lq2, lk2)."""
+    from realhf_b200.ops.functional import cached_on
+
+    def build(w):
+        f = w.float()
+        return (torch.exp((f[0] * f[1]).sum()) - torch.exp((f[2] * f[3]).sum()) + diff).reshape(1).contiguous()
+    return cached_on(w_lambda, f"_lambda_{float(diff)!r}", build)
+
+
+def _diff_view(a):
+    """The kernels' view of a differential block: every (head, map) is a head."""
+    import copy
+    v = copy.copy(a)
+    v.n_heads, v.n_kv_heads, v.n_maps = a.n_heads * 2, a.n_kv_heads * 2, 1
+    return v
+
+
+def _qk_head_norm_ref(qkv, wq, wk, nq, nk, d, eps):
+    T = qkv.shape[0]
+    x = qkv[:, : (nq + nk) * d].float().view(T, nq + nk, d)
+    x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    w = torch.cat([wq.float().expand(nq, d), wk.float().expand(nk, d)], 0)
+    qkv[:, : (nq + nk) * d] = (x * w).reshape(T, -1).to(qkv.dtype)
+
+
+def _diff_combine_ref(att, lam, H, G, dv, diff, eps, out_dtype):
+    T = att.shape[0]
+    per = H // G
+    x = att.float().view(T, G, 2, per, dv)
+    o = (x[:, :, 0] - lam.float() * x[:, :, 1]).reshape(T, H, dv)
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * (1.0 - diff)
+    return o.reshape(T, H * dv).to(out_dtype)
+
+
+def diff_window_attention(qkv, a, wq, wk, w_lambda, eps: float, k_cache, v_cache, tok_slot, pos, remain, cu_seqlens, max_seqlen=None):
+    """Packed differential attention of a block's own tokens (sequences start at position 0).  `qkv` is normalised IN PLACE
+    (query / key heads); with caches, the rows a later decode step can still see are stored.  Returns [T, H * dv] in qkv's dtype."""
+    H, G, d, dv = a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim
+    T = qkv.shape[0]
+    lam = diff_lambda(w_lambda, a.diff)
+    av = _diff_view(a)
+    win = a.window if a.window is not None else -1
+    if use_native(qkv) and d <= 512 and dv <= 256:
+        lib().qk_head_norm_(qkv, wq, wk, 2 * H, 2 * G, d, eps)
+        v_n = torch.empty(T, G * dv, dtype=qkv.dtype, device=qkv.device)
+        lib().value_norm_store(qkv, v_n, k_cache, v_cache, tok_slot if k_cache is not None else None, pos,
+                               remain if k_cache is not None else None, 2 * H, 2 * G, d, dv, a.keep_first, False, eps, 2)
+        att = torch.empty(T, 2 * H * dv, dtype=torch.float32, device=qkv.device)
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        lib().sink_window_attention(qkv, v_n, att, None, None, cu_seqlens, max_seqlen, 2 * H, 2 * G, d, dv, a.scale, win, a.keep_first, -1.0, False, 2)
+        out = torch.empty(T, H * dv, dtype=qkv.dtype, device=qkv.device)
+        lib().diff_combine(att, lam, out, H, G, dv, a.diff, eps)
+        return out
+    _qk_head_norm_ref(qkv, wq, wk, 2 * H, 2 * G, d, eps)
+    oq, ok_ = 2 * H * d, 2 * (H + G) * d
+    if k_cache is not None:
+        rows = k_cache.shape[2]
+        keep = (tok_slot >= 0) & ((pos < a.keep_first) | (remain < rows - a.keep_first))
+        r = cache_row(pos.long(), a.keep_first, rows)[keep]
+        s = tok_slot[keep].long()
+        k_cache[s, :, r] = qkv[keep, oq:ok_].view(-1, 2 * G, d)
+        v_cache[s, :, r] = qkv[keep, ok_:ok_ + G * dv].view(-1, G, dv)
+    q = qkv[:, :oq].float().view(T, 2 * H, d)
+    k = qkv[:, oq:ok_].float().view(T, 2 * G, d)
+    v = qkv[:, ok_:ok_ + G * dv].float().view(T, G, dv)
+    att = torch.zeros(T, 2 * H, dv, dtype=torch.float32, device=qkv.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        s0, e0 = cu[b], cu[b + 1]
+        L = e0 - s0
+        if L == 0:
+            continue
+        i = torch.arange(L, device=qkv.device).unsqueeze(1)
+        j = torch.arange(L, device=qkv.device).unsqueeze(0)
+        ok = j <= i
+        if a.window is not None:
+            ok = ok & ((i - j < a.window) | (j < a.keep_first))
+        for h in range(2 * H):
+            g = h // (H // G)
+            sc = (q[s0:e0, h] @ k[s0:e0, g].T) * a.scale
+            att[s0:e0, h] = _sink_softmax_pv(sc, ok, None, v[s0:e0, g // 2])
+    return _diff_combine_ref(att.reshape(T, -1), lam, H, G, dv, a.diff, eps, qkv.dtype)
+
+
+def diff_window_decode_attention(qkv, a, wq, wk, w_lambda, eps: float, k_cache, v_cache, cache_lens, slots):
+    """One new token per row: normalises the row's query / key heads in place, appends key and value at the row of position
+    cache_lens[slot] and attends to the window (both maps), then combines.  Returns [B, H * dv]."""
+    H, G, d, dv = a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim
+    B = qkv.shape[0]
+    lam = diff_lambda(w_lambda, a.diff)
+    if use_native(qkv) and dv <= 256:
+        lib().qk_head_norm_(qkv, wq, wk, 2 * H, 2 * G, d, eps)
+        att = torch.empty(B, 2 * H * dv, dtype=torch.float32, device=qkv.device)
+        lib().sink_window_decode_attention(qkv, att, None, None, k_cache, v_cache, cache_lens, slots, 2 * H, 2 * G, d, dv, a.scale,
+                                           a.window if a.window is not None else -1, a.keep_first, -1.0, False, False, eps, 2)
+        out = torch.empty(B, H * dv, dtype=qkv.dtype, device=qkv.device)
+        lib().diff_combine(att, lam, out, H, G, dv, a.diff, eps)
+        return out
+    _qk_head_norm_ref(qkv, wq, wk, 2 * H, 2 * G, d, eps)
+    oq, ok_ = 2 * H * d, 2 * (H + G) * d
+    rows = k_cache.shape[2]
+    att = torch.zeros(B, 2 * H, dv, dtype=torch.float32, device=qkv.device)
+    for b in range(B):
+        s = int(slots[b]) if slots is not None else b
+        n = int(cache_lens[s])
+        r = cache_row(n, a.keep_first, rows)
+        k_cache[s, :, r] = qkv[b, oq:ok_].view(2 * G, d)
+        v_cache[s, :, r] = qkv[b, ok_:ok_ + G * dv].view(G, dv)
+        j = torch.arange(n + 1, device=qkv.device)
+        if a.window is not None:
+            j = j[(n - j < a.window) | (j < a.keep_first)]
+        rj = cache_row(j, a.keep_first, rows)
+        kk = k_cache[s][:, rj].float()
+        vv = v_cache[s][:, rj].float()
+        q = qkv[b, :oq].float().view(2 * H, d)
+        for h in range(2 * H):
+            g = h // (H // G)
+            att[b, h] = torch.softmax((kk[g] @ q[h]) * a.scale, -1) @ vv[g // 2]
+    return _diff_combine_ref(att.reshape(B, -1), lam, H, G, dv, a.diff, eps, qkv.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ rotated latent attention
+# (`LatentAttentionConfig` with rot_dim / q_rank / sink / out_gate).  The input projection row is
+# [query latent (q_rank) | latent (kv_rank) | rotated key part (rot_dim) | gate logits (H x dv)]; a cache row is [c | k_rot].
+
+_ROPE_TABLES: dict = {}
+
+
+def rotary_table(rot, device):
+    """(fp32 frequencies [dims / 2] on `device`, rounded once from double precision; factor on cos / sin)."""
+    key = (rot.dims, rot.base, rot.factor, rot.original, rot.fast, rot.slow, str(device))
+    hit = _ROPE_TABLES.get(key)
+    if hit is None:
+        f, m = rot.frequencies()
+        hit = _ROPE_TABLES[key] = (torch.tensor(f, dtype=torch.float64).float().to(device), float(m))
+    return hit
+
+
+def _rotate_ref(x, pos, inv_freq, mscale):
+    """x [N, ..., rot] fp32, pos [N]: interleaved pairs turn by pos * f_i (fp32)."""
+    ang = pos.float().unsqueeze(-1) * inv_freq
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [inv_freq.numel()]
+    cs, sn = (torch.cos(ang) * mscale).view(shape), (torch.sin(ang) * mscale).view(shape)
+    u, v = x[..., 0::2], x[..., 1::2]
+    return torch.stack([u * cs - v * sn, v * cs + u * sn], -1).flatten(-2)
+
+
+def latent_rope_prepare(proj, a, wq, wc, eps: float, pos, cache, tok_slot=None, remain=None, cache_lens=None, slots=None, want_lat=True):
+    """From the input projection: cq = RMSNorm(query latent) * wq ([T, q_rank], None without a query latent) and the row
+    [c | k_rot] = [RMSNorm(latent) * wc | rotate(key part)] ([T, kv_rank + rot_dim], with `want_lat`), also written to the ring
+    cache.  Packed form (`pos` [T]): the tokens with tok_slot >= 0 among the last R of their sequence are stored; step form
+    (`pos` None): row b's position is cache_lens[slot], and its row is stored."""
+    T = proj.shape[0]
+    qr, r, rot = a.q_rank or 0, a.kv_rank, a.rot_dim
+    inv_freq, ms = rotary_table(a.rotary, proj.device) if rot else (torch.zeros(1, device=proj.device), 1.0)
+    if use_native(proj):
+        cq = torch.empty(T, qr, dtype=proj.dtype, device=proj.device) if qr else None
+        lat = torch.empty(T, r + rot, dtype=proj.dtype, device=proj.device) if want_lat else None
+        lib().latent_rope_prepare(proj, wq if qr else None, wc, inv_freq, ms, pos, cache_lens if pos is None else None,
+                                  slots if pos is None else None, tok_slot if (cache is not None and pos is not None) else None,
+                                  remain if (cache is not None and pos is not None) else None, cq, lat, cache, qr, r, rot, eps)
+        return cq, lat
+    cq = None
+    if qr:
+        x = proj[:, :qr].float()
+        cq = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * wq.float()).to(proj.dtype)
+    c = proj[:, qr:qr + r].float()
+    c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * wc.float()
+    if pos is None:
+        idx = slots.long() if slots is not None else torch.arange(T, device=proj.device)
+        p = cache_lens[idx]
+    else:
+        p = pos
+    parts = [c]
+    if rot:
+        parts.append(_rotate_ref(proj[:, qr + r:qr + r + rot].float(), p, inv_freq, ms))
+    lat = torch.cat(parts, -1).to(proj.dtype)
+    if cache is not None:
+        R = cache.shape[1]
+        if pos is None:
+            cache[idx, (p % R).long()] = lat
+        else:
+            keep = (tok_slot >= 0) & (remain < R)
+            cache[tok_slot[keep].long(), (pos[keep] % R).long()] = lat[keep]
+    return cq, lat
+
+
+def latent_rope_attention(q, kv, lat, a, sink, pos, cu_seqlens, max_seqlen=None):
+    """Packed causal attention: q [T, H (d + rot)] (rotated here), kv [T, H d | H dv] the up-projected unrotated keys and values,
+    lat [T, kv_rank + rot] whose last rot columns are the rotated key part of every head.  The softmax denominator holds
+    exp(sink_h) when `sink` is given.  Returns [T, H * dv] in q's dtype."""
+    T = q.shape[0]
+    H, d, rot, dv, r = a.n_heads, a.qk_dim, a.rot_dim, a.v_dim, a.kv_rank
+    dq = d + rot
+    inv_freq, ms = rotary_table(a.rotary, q.device) if rot else (torch.zeros(1, device=q.device), 1.0)
+    if use_native(q) and dq <= 512 and dv <= 256:
+        qk = torch.empty(T, 2 * H * dq, dtype=q.dtype, device=q.device)
+        lib().latent_rope_assemble(q, kv, lat, pos, inv_freq, ms, qk, H, d, rot, r)
+        out = torch.empty(T, H * dv, dtype=q.dtype, device=q.device)
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        lib().sink_window_attention(qk, kv[:, H * d:], out, None, sink, cu_seqlens, max_seqlen, H, H, dq, dv, a.scale, -1, 0, -1.0, False, 1)
+        return out
+    qh = q.float().view(T, H, dq)
+    if rot:
+        qh = torch.cat([qh[..., :d], _rotate_ref(qh[..., d:], pos, inv_freq, ms).to(q.dtype).float()], -1)
+    kh = torch.cat([kv[:, : H * d].float().view(T, H, d), lat[:, r:].float().unsqueeze(1).expand(T, H, rot)], -1)
+    vh = kv[:, H * d:].float().view(T, H, dv)
+    out = torch.zeros(T, H, dv, dtype=torch.float32, device=q.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        s0, e0 = cu[b], cu[b + 1]
+        L = e0 - s0
+        if L == 0:
+            continue
+        ok = torch.arange(L, device=q.device).unsqueeze(0) <= torch.arange(L, device=q.device).unsqueeze(1)
+        for h in range(H):
+            sc = (qh[s0:e0, h] @ kh[s0:e0, h].T) * a.scale
+            out[s0:e0, h] = _sink_softmax_pv(sc, ok, sink[h].float() if sink is not None else None, vh[s0:e0, h])
+    return out.reshape(T, H * dv).to(q.dtype)
+
+
+def latent_rope_decode_attention(q, a, w_ukv, sink, cache, cache_lens, slots):
+    """One new token per row against the cached rows [c | k_rot] of its slot (the row of the new token is already stored).  Keys
+    and values are never formed: score_j = scale (q_nope W_uk) . c_j + scale rotate(q_rot) . k_rot_j, the weighted sum of the cached
+    latents comes back through W_uv.  Returns [B, H * dv] in q's dtype."""
+    B = q.shape[0]
+    H, d, rot, dv, r = a.n_heads, a.qk_dim, a.rot_dim, a.v_dim, a.kv_rank
+    dq = d + rot
+    inv_freq, ms = rotary_table(a.rotary, q.device) if rot else (torch.zeros(1, device=q.device), 1.0)
+    wk, wv = _absorbed_projections(w_ukv, H, d, dv, a.scale)
+    R = cache.shape[1]
+    if use_native(q) and r + rot <= 512:
+        from realhf_b200.ops.functional import cached_on
+        qa = torch.empty(H, B, r + rot, dtype=torch.float32, device=q.device)
+        qa[:, :, :r] = torch.bmm(q.view(B, H, dq)[:, :, :d].transpose(0, 1).float(), wk)
+        if rot:
+            lib().latent_query_rope(q, cache_lens, slots, inv_freq, ms, a.scale, qa, d, rot)
+        ctas = B * ((H + 15) // 16)
+        splits = max(1, min((3 * 148 + ctas - 1) // ctas, R // 64, 32))
+        sk = cached_on(sink, "_f32", lambda w: w.float().contiguous()) if sink is not None else None
+        o = lib().latent_decode_core(qa, cache, cache_lens, slots, 0, splits, sk)
+        return torch.bmm(o[:, :, :r], wv).transpose(0, 1).reshape(B, H * dv).to(q.dtype)
+    idx = slots.long() if slots is not None else torch.arange(B, device=q.device)
+    pos = cache_lens[idx]
+    qh = q.float().view(B, H, dq)
+    qa = torch.einsum("bhd,hdr->bhr", qh[..., :d], wk)
+    if rot:
+        qa = torch.cat([qa, _rotate_ref(qh[..., d:], pos, inv_freq, ms) * a.scale], -1)
+    out = torch.empty(B, H * dv, dtype=torch.float32, device=q.device)
+    for b in range(B):
+        p = int(pos[b])
+        cw = cache[idx[b], torch.arange(0, p + 1, device=q.device) % R].float()
+        sc = qa[b] @ cw.t()
+        pr = _sink_softmax_pv(sc, torch.ones_like(sc, dtype=torch.bool), sink.float().unsqueeze(-1) if sink is not None else None, cw[:, :r])
+        out[b] = torch.einsum("hr,hrv->hv", pr, wv).reshape(-1)
+    return out.to(q.dtype)
+
+
+def sigmoid_gate_(x, gate):
+    """x[t, c] *= sigmoid(gate[t, c]) in place (fp32 inside); gate may be a column slice of a wider projection."""
+    if use_native(x):
+        lib().sigmoid_gate_(x, gate)
+        return x
+    x.copy_((x.float() * torch.sigmoid(gate[:, : x.shape[1]].float())).to(x.dtype))
+    return x

@@ -308,6 +308,7 @@ void register_attn_ops(torch::Library& m);     // bindings_attn.cpp
 void register_comm_ops(torch::Library& m);
 void register_seq_ops(torch::Library& m);      // bindings_seq.cpp
 void register_state_ops(torch::Library& m);    // bindings_state.cpp
+void register_mix_ops(torch::Library& m);      // bindings_mix.cpp
 
 static int64_t set_pdl(int64_t on) { const int old = rb_get_pdl(); if (on >= 0) rb_set_pdl((int)on); return old; }
 
@@ -333,4 +334,5 @@ TORCH_LIBRARY(realhf_b200, m) {
   register_comm_ops(m);
   register_seq_ops(m);
   register_state_ops(m);
+  register_mix_ops(m);
 }

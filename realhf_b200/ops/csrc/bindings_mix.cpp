@@ -1,0 +1,193 @@
+// torch.ops.realhf_b200.* registrations of the matrix-memory LSTM (mlstm.cu), the rotated latent attention helpers (latent_rope.cu)
+// and the query / key head norm and differential combine of window attention (sinkattn.cu).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/types.h>
+
+using at::Tensor;
+using OptT = c10::optional<Tensor>;
+
+#define CHECK_CUDA(x) TORCH_CHECK((x).is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_IN(x) \
+  CHECK_CUDA(x);    \
+  TORCH_CHECK((x).is_contiguous(), #x " must be contiguous")
+#define CHECK_ROWS(x) \
+  CHECK_CUDA(x);      \
+  TORCH_CHECK((x).dim() == 2 && (x).stride(1) == 1, #x " must be 2-D with unit column stride")
+
+static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+static inline int dt_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kBFloat16: return 1;
+    case at::kHalf: return 2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+}
+static inline const int* int_ptr(const OptT& t, int64_t n, const char* what) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kInt && t->numel() >= n, what, ": int32 CUDA tensor expected");
+  return t->data_ptr<int>();
+}
+
+extern "C" {
+int rb_mlstm_scan(const void*, int64_t, int, const void*, float*, float*, const int*, float*, float*, const int*, int, int, int, int, int, int, int, float,
+                  float, int, cudaStream_t);
+int rb_mlstm_out(const float*, const float*, const void*, int, const void*, int64_t, int, void*, int, int64_t, int, int, float, cudaStream_t);
+int rb_latent_rope_prepare(const void*, int64_t, int, const void*, const void*, const float*, float, const int*, const int*, const int*, const int*,
+                           const int*, void*, void*, void*, int64_t, int, int, int, int, float, cudaStream_t);
+int rb_latent_rope_assemble(const void*, int64_t, const void*, int64_t, const void*, int64_t, int, const int*, const float*, float, void*, int, int64_t,
+                            int, int, int, cudaStream_t);
+int rb_latent_query_rope(const void*, int64_t, int, const int*, const int*, const float*, float, float, float*, int, int, int, int, int, cudaStream_t);
+int rb_sigmoid_gate(void*, int, const void*, int64_t, int, int64_t, int, cudaStream_t);
+int rb_qk_head_norm(void*, int64_t, int, const void*, const void*, int64_t, int, int, int, float, cudaStream_t);
+int rb_diff_combine(const void*, int, const float*, void*, int, int64_t, int, int, int, float, float, cudaStream_t);
+}
+
+namespace {
+
+// proj [T, ld] = [q (H d) | k (H d) | v (H dv) | output gate (H dv) | x_i (H), x_f (H), padding]; cu absent: decode step (row b =
+// sequence b); state [n_slots, H, d, dv + 1] fp32 and m_state [n_slots, H] fp32 or absent.  o [T, H, dv + 1], m_out [T, H] fp32.
+void mlstm_scan(const Tensor& proj, const Tensor& gate_bias, Tensor o, Tensor m_out, const OptT& cu, const OptT& state, const OptT& m_state,
+                const OptT& slots, int64_t H, int64_t d, int64_t dv, double cap, bool load_state) {
+  CHECK_ROWS(proj); CHECK_IN(gate_bias); CHECK_IN(o); CHECK_IN(m_out);
+  const int64_t T = proj.size(0);
+  const int64_t off_k = H * d, off_v = 2 * H * d, off_if = 2 * H * d + 2 * H * dv;
+  TORCH_CHECK(proj.size(1) >= off_if + 2 * H && gate_bias.numel() == 2 * H && gate_bias.scalar_type() == proj.scalar_type());
+  TORCH_CHECK(o.scalar_type() == at::kFloat && m_out.scalar_type() == at::kFloat && o.numel() == T * H * (dv + 1) && m_out.numel() == T * H);
+  int n_seqs = (int)T;
+  const int* cup = nullptr;
+  if (cu.has_value()) {
+    CHECK_IN((*cu));
+    TORCH_CHECK(cu->scalar_type() == at::kInt && cu->numel() >= 1);
+    cup = cu->data_ptr<int>();
+    n_seqs = (int)cu->numel() - 1;
+  }
+  float *sp = nullptr, *mp = nullptr;
+  if (state.has_value()) {
+    CHECK_IN((*state)); CHECK_IN((*m_state));
+    TORCH_CHECK(state->scalar_type() == at::kFloat && state->dim() == 4 && state->size(1) == H && state->size(2) == d && state->size(3) == dv + 1);
+    TORCH_CHECK(m_state->scalar_type() == at::kFloat && m_state->numel() == state->size(0) * H);
+    TORCH_CHECK(slots.has_value() || state->size(0) >= n_seqs);
+    sp = state->data_ptr<float>(); mp = m_state->data_ptr<float>();
+  }
+  TORCH_CHECK(!load_state || sp != nullptr, "load_state needs the state");
+  c10::cuda::CUDAGuard g(proj.device());
+  const int rc = rb_mlstm_scan(proj.data_ptr(), proj.stride(0), dt_code(proj), gate_bias.data_ptr(), o.data_ptr<float>(), m_out.data_ptr<float>(), cup, sp,
+                               mp, int_ptr(slots, n_seqs, "slots"), n_seqs, (int)H, (int)d, (int)dv, (int)off_k, (int)off_v, (int)off_if, (float)cap,
+                               (float)(1.0 / std::sqrt((double)d)), load_state ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "mlstm_scan: unsupported shape (rc ", rc, ")");
+}
+
+void mlstm_out(const Tensor& o, const Tensor& m, const Tensor& w, const Tensor& gate, Tensor out, double eps) {
+  CHECK_IN(o); CHECK_IN(m); CHECK_IN(w); CHECK_ROWS(gate); CHECK_IN(out);
+  TORCH_CHECK(o.dim() == 3 && o.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat);
+  const int64_t T = o.size(0), H = o.size(1), dv = o.size(2) - 1;
+  TORCH_CHECK(m.numel() == T * H && w.numel() == H * dv && gate.size(0) == T && gate.size(1) >= H * dv && out.numel() == T * H * dv);
+  c10::cuda::CUDAGuard g(o.device());
+  TORCH_CHECK(rb_mlstm_out(o.data_ptr<float>(), m.data_ptr<float>(), w.data_ptr(), dt_code(w), gate.data_ptr(), gate.stride(0), dt_code(gate),
+                           out.data_ptr(), dt_code(out), T, (int)H, (int)dv, (float)eps, cur_stream()) == 0);
+}
+
+// pos given: packed form (cache / tok_slot / remain optional); pos absent: step form (position lens[slot], the cache row is written)
+void latent_rope_prepare(const Tensor& proj, const OptT& wq, const Tensor& wc, const Tensor& inv_freq, double mscale, const OptT& pos, const OptT& lens,
+                         const OptT& slots, const OptT& tok_slot, const OptT& remain, const OptT& cq, const OptT& lat, const OptT& cache, int64_t q_rank,
+                         int64_t r, int64_t rot, double eps) {
+  CHECK_ROWS(proj); CHECK_IN(wc); CHECK_IN(inv_freq);
+  const int64_t T = proj.size(0);
+  TORCH_CHECK(proj.size(1) >= q_rank + r + rot && wc.numel() == r && wc.scalar_type() == proj.scalar_type());
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.numel() >= rot / 2 && rot % 2 == 0);
+  const void* wqp = nullptr;
+  void *cqp = nullptr, *latp = nullptr, *cachep = nullptr;
+  if (q_rank > 0) {
+    TORCH_CHECK(wq.has_value() && cq.has_value());
+    CHECK_IN((*wq)); CHECK_IN((*cq));
+    TORCH_CHECK(wq->numel() == q_rank && wq->scalar_type() == proj.scalar_type() && cq->numel() == T * q_rank && cq->scalar_type() == proj.scalar_type());
+    wqp = wq->data_ptr(); cqp = cq->data_ptr();
+  }
+  if (lat.has_value()) {
+    CHECK_IN((*lat));
+    TORCH_CHECK(lat->numel() == T * (r + rot) && lat->scalar_type() == proj.scalar_type());
+    latp = lat->data_ptr();
+  }
+  int R = 1;
+  if (cache.has_value()) {
+    CHECK_IN((*cache));
+    TORCH_CHECK(cache->dim() == 3 && cache->size(2) == r + rot && cache->scalar_type() == proj.scalar_type());
+    R = (int)cache->size(1);
+    cachep = cache->data_ptr();
+    TORCH_CHECK(pos.has_value() ? (tok_slot.has_value() && remain.has_value()) : (slots.has_value() || cache->size(0) >= T));
+  }
+  TORCH_CHECK(pos.has_value() || lens.has_value(), "positions: `pos` (packed) or `lens` (step)");
+  c10::cuda::CUDAGuard g(proj.device());
+  const int rc = rb_latent_rope_prepare(proj.data_ptr(), proj.stride(0), dt_code(proj), wqp, wc.data_ptr(), inv_freq.data_ptr<float>(), (float)mscale,
+                                        int_ptr(pos, T, "pos"), pos.has_value() ? nullptr : int_ptr(lens, 1, "lens"),
+                                        pos.has_value() ? nullptr : int_ptr(slots, T, "slots"),
+                                        cachep && pos.has_value() ? int_ptr(tok_slot, T, "tok_slot") : nullptr,
+                                        cachep && pos.has_value() ? int_ptr(remain, T, "remain") : nullptr, cqp, latp, cachep, T, (int)q_rank, (int)r,
+                                        (int)rot, R, (float)eps, cur_stream());
+  TORCH_CHECK(rc == 0, "latent_rope_prepare: unsupported shape (rc ", rc, ")");
+}
+
+void latent_rope_assemble(const Tensor& q, const Tensor& kn, const Tensor& lat, const Tensor& pos, const Tensor& inv_freq, double mscale, Tensor out,
+                          int64_t H, int64_t d, int64_t rot, int64_t r) {
+  CHECK_ROWS(q); CHECK_ROWS(kn); CHECK_ROWS(lat); CHECK_IN(pos); CHECK_IN(inv_freq); CHECK_IN(out);
+  const int64_t T = q.size(0);
+  TORCH_CHECK(q.size(1) >= H * (d + rot) && kn.size(1) >= H * d && lat.size(1) >= r + rot && out.numel() == T * 2 * H * (d + rot));
+  TORCH_CHECK(kn.scalar_type() == q.scalar_type() && lat.scalar_type() == q.scalar_type() && out.scalar_type() == q.scalar_type());
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.numel() >= rot / 2);
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(rb_latent_rope_assemble(q.data_ptr(), q.stride(0), kn.data_ptr(), kn.stride(0), lat.data_ptr(), lat.stride(0), (int)r,
+                                      int_ptr(pos, T, "pos"), inv_freq.data_ptr<float>(), (float)mscale, out.data_ptr(), dt_code(q), T, (int)H, (int)d,
+                                      (int)rot, cur_stream()) == 0);
+}
+
+// qa [H, B, r + rot] fp32: columns [r, r + rot) <- scale * rotate(q[b, h, d:])
+void latent_query_rope(const Tensor& q, const Tensor& lens, const OptT& slots, const Tensor& inv_freq, double mscale, double scale, Tensor qa,
+                       int64_t d, int64_t rot) {
+  CHECK_ROWS(q); CHECK_IN(lens); CHECK_IN(inv_freq); CHECK_IN(qa);
+  TORCH_CHECK(qa.dim() == 3 && qa.scalar_type() == at::kFloat && qa.size(1) == q.size(0) && qa.size(2) > rot);
+  const int64_t H = qa.size(0), B = qa.size(1), r = qa.size(2) - rot;
+  TORCH_CHECK(q.size(1) >= H * (d + rot) && inv_freq.scalar_type() == at::kFloat && inv_freq.numel() >= rot / 2);
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(rb_latent_query_rope(q.data_ptr(), q.stride(0), dt_code(q), int_ptr(lens, 1, "lens"), int_ptr(slots, B, "slots"),
+                                   inv_freq.data_ptr<float>(), (float)mscale, (float)scale, qa.data_ptr<float>(), (int)B, (int)H, (int)d, (int)rot, (int)r,
+                                   cur_stream()) == 0);
+}
+
+void sigmoid_gate_(Tensor x, const Tensor& gate) {
+  CHECK_IN(x); CHECK_ROWS(gate);
+  TORCH_CHECK(x.dim() == 2 && gate.size(0) == x.size(0) && gate.size(1) >= x.size(1));
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(rb_sigmoid_gate(x.data_ptr(), dt_code(x), gate.data_ptr(), gate.stride(0), dt_code(gate), x.size(0), (int)x.size(1), cur_stream()) == 0);
+}
+
+void qk_head_norm_(Tensor x, const Tensor& wq, const Tensor& wk, int64_t nq, int64_t nk, int64_t d, double eps) {
+  CHECK_ROWS(x); CHECK_IN(wq); CHECK_IN(wk);
+  TORCH_CHECK(x.size(1) >= (nq + nk) * d && wq.numel() == d && wk.numel() == d && wq.scalar_type() == x.scalar_type() && wk.scalar_type() == x.scalar_type());
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(rb_qk_head_norm(x.data_ptr(), x.stride(0), dt_code(x), wq.data_ptr(), wk.data_ptr(), x.size(0), (int)nq, (int)nk, (int)d, (float)eps,
+                              cur_stream()) == 0);
+}
+
+void diff_combine(const Tensor& a, const Tensor& lam, Tensor out, int64_t H, int64_t G, int64_t dv, double diff, double eps) {
+  CHECK_IN(a); CHECK_IN(lam); CHECK_IN(out);
+  TORCH_CHECK(lam.scalar_type() == at::kFloat && lam.numel() == 1 && a.numel() == 2 * out.numel() && out.numel() % (H * dv) == 0 && H % G == 0);
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(rb_diff_combine(a.data_ptr(), dt_code(a), lam.data_ptr<float>(), out.data_ptr(), dt_code(out), out.numel() / (H * dv), (int)H, (int)G,
+                              (int)dv, (float)diff, (float)eps, cur_stream()) == 0);
+}
+
+}  // namespace
+
+void register_mix_ops(torch::Library& m) {
+  m.def("mlstm_scan(Tensor proj, Tensor gate_bias, Tensor(a!) o, Tensor(b!) m_out, Tensor? cu, Tensor(c!)? state, Tensor(d!)? m_state, Tensor? slots, int H, int d, int dv, float cap, bool load_state) -> ()", &mlstm_scan);
+  m.def("mlstm_out(Tensor o, Tensor m, Tensor w, Tensor gate, Tensor(a!) out, float eps) -> ()", &mlstm_out);
+  m.def("latent_rope_prepare(Tensor proj, Tensor? wq, Tensor wc, Tensor inv_freq, float mscale, Tensor? pos, Tensor? lens, Tensor? slots, Tensor? tok_slot, Tensor? remain, Tensor(a!)? cq, Tensor(b!)? lat, Tensor(c!)? cache, int q_rank, int r, int rot, float eps) -> ()", &latent_rope_prepare);
+  m.def("latent_rope_assemble(Tensor q, Tensor kn, Tensor lat, Tensor pos, Tensor inv_freq, float mscale, Tensor(a!) out, int H, int d, int rot, int r) -> ()", &latent_rope_assemble);
+  m.def("latent_query_rope(Tensor q, Tensor lens, Tensor? slots, Tensor inv_freq, float mscale, float scale, Tensor(a!) qa, int d, int rot) -> ()", &latent_query_rope);
+  m.def("sigmoid_gate_(Tensor(a!) x, Tensor gate) -> ()", &sigmoid_gate_);
+  m.def("qk_head_norm_(Tensor(a!) x, Tensor wq, Tensor wk, int nq, int nk, int d, float eps) -> ()", &qk_head_norm_);
+  m.def("diff_combine(Tensor a, Tensor lam, Tensor(a!) out, int H, int G, int dv, float diff, float eps) -> ()", &diff_combine);
+}

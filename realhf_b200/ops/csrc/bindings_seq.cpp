@@ -42,7 +42,7 @@ int rb_latent_window_attention(const void*, int64_t, const void*, int64_t, const
 int rb_latent_decode_attention(const void*, int64_t, const void*, const void*, void*, const int*, const int*, void*, int, int, int, int, int,
                                int, float, int, float, int, cudaStream_t);
 int rb_latent_append(const void*, int64_t, int, const void*, void*, const int*, const int*, int, int, int, float, int, cudaStream_t);
-int rb_latent_decode_core(const float*, const void*, const int*, const int*, float*, float*, float*, int, int, int, int, int, int, int,
+int rb_latent_decode_core(const float*, const void*, const int*, const int*, float*, float*, float*, int, int, int, int, int, int, int, const float*,
                           cudaStream_t);
 }
 
@@ -209,12 +209,14 @@ void latent_append(const Tensor& qc, int64_t n_q, const Tensor& w_ln, Tensor cac
 }
 
 // qa [H, B, rank] fp32 (queries in latent space, scale applied) -> softmax-weighted sums of the cached latents [H, B, rank] fp32.
-Tensor latent_decode_core(const Tensor& qa, const Tensor& cache, const Tensor& cache_lens, const OptT& slots, int64_t window, int64_t splits) {
+Tensor latent_decode_core(const Tensor& qa, const Tensor& cache, const Tensor& cache_lens, const OptT& slots, int64_t window, int64_t splits,
+                         const OptT& sink) {
   CHECK_IN(qa); CHECK_IN(cache); CHECK_IN(cache_lens);
   TORCH_CHECK(qa.dim() == 3 && qa.scalar_type() == at::kFloat && cache.dim() == 3 && cache.size(2) == qa.size(2));
   TORCH_CHECK(cache_lens.scalar_type() == at::kInt);
   const int64_t H = qa.size(0), B = qa.size(1), rank = qa.size(2);
   TORCH_CHECK(slots.has_value() || cache.size(0) >= B);
+  if (sink.has_value()) TORCH_CHECK(sink->is_cuda() && sink->is_contiguous() && sink->scalar_type() == at::kFloat && sink->numel() == H, "sink: fp32 [H]");
   c10::cuda::CUDAGuard g(qa.device());
   auto out = at::empty_like(qa);
   Tensor pa, pm;
@@ -225,7 +227,7 @@ Tensor latent_decode_core(const Tensor& qa, const Tensor& cache, const Tensor& c
   const int rc = rb_latent_decode_core(qa.data_ptr<float>(), cache.data_ptr(), cache_lens.data_ptr<int>(), int_ptr(slots, B, "slots"),
                                        out.data_ptr<float>(), splits > 1 ? pa.data_ptr<float>() : nullptr,
                                        splits > 1 ? pm.data_ptr<float>() : nullptr, (int)B, (int)H, (int)rank, (int)cache.size(1), (int)window,
-                                       (int)splits, dt_code(cache), cur_stream());
+                                       (int)splits, dt_code(cache), sink.has_value() ? sink->data_ptr<float>() : nullptr, cur_stream());
   TORCH_CHECK(rc == 0, "latent_decode_core: unsupported shape (rc ", rc, ")");
   return out;
 }
@@ -241,6 +243,6 @@ void register_seq_ops(torch::Library& m) {
   m.def("latent_norm_store(Tensor qc, int n_q, Tensor w_ln, float eps, Tensor(a!)? cache, Tensor? tok_slot, Tensor pos, Tensor? remain) -> Tensor", &latent_norm_store);
   m.def("latent_window_attention(Tensor q, Tensor kv, Tensor pos, int n_heads, int qk, int vd, float scale, int window) -> Tensor", &latent_window_attention);
   m.def("latent_append(Tensor qc, int n_q, Tensor w_ln, Tensor(a!) cache, Tensor cache_lens, Tensor? slots, float eps) -> ()", &latent_append);
-  m.def("latent_decode_core(Tensor qa, Tensor cache, Tensor cache_lens, Tensor? slots, int window, int splits) -> Tensor", &latent_decode_core);
+  m.def("latent_decode_core(Tensor qa, Tensor cache, Tensor cache_lens, Tensor? slots, int window, int splits, Tensor? sink=None) -> Tensor", &latent_decode_core);
   m.def("latent_decode_attention(Tensor qc, Tensor? w_ln, Tensor w_ukv, Tensor(a!) cache, Tensor cache_lens, Tensor? slots, int n_heads, int qk, int vd, float scale, int window, float eps) -> Tensor", &latent_decode_attention);
 }

@@ -40,13 +40,13 @@ extern "C" {
 int rb_embed_sinusoid(const int64_t*, const void*, int, const int*, const int*, const float*, float*, int64_t, int, int, cudaStream_t);
 int rb_concat_cast(const void*, int, int, const void*, int, int, void*, int, int64_t, cudaStream_t);
 int rb_relu2(const void*, void*, int, int64_t, cudaStream_t);
-int rb_rms_norm_rows(void*, int, const void*, int, const void*, int, void*, int, int64_t, int, float, cudaStream_t);
+int rb_rms_norm_rows(void*, int, const void*, int, const void*, int, void*, int, int64_t, int, float, float, cudaStream_t);
 int rb_value_norm_store(const void*, int64_t, int, void*, void*, void*, const int*, const int*, const int*, int64_t, int, int, int, int, int, int, int,
-                        float, cudaStream_t);
+                        float, int, cudaStream_t);
 int rb_sink_window_prefill(const void*, int64_t, const void*, void*, const void*, const void*, const int*, int, int, int, int, int, int, float, int,
-                           int, float, int, int, cudaStream_t);
+                           int, float, int, int, int, int64_t, int, cudaStream_t);
 int rb_sink_window_decode(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, int, int, int, int, int, int,
-                          float, int, int, float, int, int, float, int, cudaStream_t);
+                          float, int, int, float, int, int, float, int, int, int, cudaStream_t);
 int rb_sink_window_decode_fast(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, float*, float*, int, int,
                                int, int, int, int, float, int, int, float, int, int, float, int, cudaStream_t);
 int rb_attn_fwd_sink(const void*, const void*, const void*, void*, const int*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, float,
@@ -86,47 +86,53 @@ Tensor relu2(const Tensor& x) {
   return out;
 }
 
-// out = rmsnorm(x) * w; with y: x += y in place first
-void rms_norm_rows(Tensor x, const OptT& y, const Tensor& w, Tensor out, double eps) {
+// out = rmsnorm(x) * (w + w_offset); with y: x += y in place first
+void rms_norm_rows(Tensor x, const OptT& y, const Tensor& w, Tensor out, double eps, double w_offset) {
   CHECK_IN(x); CHECK_IN(w); CHECK_IN(out);
   const int W = x.size(-1);
   TORCH_CHECK(w.numel() == W && out.numel() == x.numel());
   if (y.has_value()) { CHECK_IN((*y)); TORCH_CHECK(y->numel() == x.numel()); }
   c10::cuda::CUDAGuard g(x.device());
   TORCH_CHECK(rb_rms_norm_rows(x.data_ptr(), dt_code(x), y.has_value() ? y->data_ptr() : nullptr, y.has_value() ? dt_code(*y) : 0, w.data_ptr(),
-                               dt_code(w), out.data_ptr(), dt_code(out), x.numel() / W, W, (float)eps, cur_stream()) == 0);
+                               dt_code(w), out.data_ptr(), dt_code(out), x.numel() / W, W, (float)eps, (float)w_offset, cur_stream()) == 0);
 }
 
-// caches: kc [n_slots, G, rows, d], vc [n_slots, G, rows, dv]
+// caches: kc [n_slots, G, rows, d], vc [n_slots, G / vshare, rows, dv] (vshare consecutive key heads read one value head)
 void value_norm_store(const Tensor& qkvg, Tensor vout, const OptT& kc, const OptT& vc, const OptT& tok_slot, const Tensor& pos, const OptT& remain,
-                      int64_t H, int64_t G, int64_t d, int64_t dv, int64_t keep, bool do_norm, double eps) {
+                      int64_t H, int64_t G, int64_t d, int64_t dv, int64_t keep, bool do_norm, double eps, int64_t vshare) {
   CHECK_ROWS(qkvg); CHECK_IN(vout);
   const int64_t T = qkvg.size(0);
-  TORCH_CHECK(qkvg.size(1) >= H * d + G * (d + dv) && vout.numel() == T * G * dv && vout.scalar_type() == qkvg.scalar_type());
+  TORCH_CHECK(vshare >= 1 && G % vshare == 0);
+  const int64_t Gv = G / vshare;
+  TORCH_CHECK(qkvg.size(1) >= H * d + G * d + Gv * dv && vout.numel() == T * Gv * dv && vout.scalar_type() == qkvg.scalar_type());
   int rows = 1;
   void *kp = nullptr, *vp = nullptr;
   if (kc.has_value()) {
     CHECK_IN((*kc)); CHECK_IN((*vc));
-    TORCH_CHECK(kc->dim() == 4 && kc->size(1) == G && kc->size(3) == d && vc->size(1) == G && vc->size(3) == dv && vc->size(2) == kc->size(2));
+    TORCH_CHECK(kc->dim() == 4 && kc->size(1) == G && kc->size(3) == d && vc->size(1) == Gv && vc->size(3) == dv && vc->size(2) == kc->size(2));
     TORCH_CHECK(kc->scalar_type() == qkvg.scalar_type() && vc->scalar_type() == qkvg.scalar_type() && tok_slot.has_value() && remain.has_value());
     rows = kc->size(2); kp = kc->data_ptr(); vp = vc->data_ptr();
   }
   c10::cuda::CUDAGuard g(qkvg.device());
   TORCH_CHECK(rb_value_norm_store(qkvg.data_ptr(), qkvg.stride(0), dt_code(qkvg), vout.data_ptr(), kp, vp, kp ? int_ptr(tok_slot, T, "tok_slot") : nullptr,
                                   int_ptr(pos, T, "pos"), kp ? int_ptr(remain, T, "remain") : nullptr, T, (int)H, (int)G, (int)d, (int)dv, (int)keep, rows,
-                                  do_norm ? 1 : 0, (float)eps, cur_stream()) == 0);
+                                  do_norm ? 1 : 0, (float)eps, (int)vshare, cur_stream()) == 0);
 }
 
 void sink_window_attention(const Tensor& qkvg, const Tensor& vn, Tensor out, const OptT& temp, const OptT& sink, const Tensor& cu, int64_t max_seqlen,
-                           int64_t H, int64_t G, int64_t d, int64_t dv, double scale, int64_t window, int64_t keep, double slope_base, bool gate) {
-  CHECK_ROWS(qkvg); CHECK_IN(vn); CHECK_IN(out); CHECK_IN(cu);
+                           int64_t H, int64_t G, int64_t d, int64_t dv, double scale, int64_t window, int64_t keep, double slope_base, bool gate,
+                           int64_t vshare) {
+  // vn: rows of G / vshare value heads (any row stride); out in its own type (fp32 keeps the weighted sums unrounded)
+  CHECK_ROWS(qkvg); CHECK_ROWS(vn); CHECK_IN(out); CHECK_IN(cu);
   const int64_t T = qkvg.size(0);
-  TORCH_CHECK(qkvg.size(1) >= H * d + G * (d + dv) + (gate ? H : 0) && vn.numel() == T * G * dv && out.numel() == T * H * dv);
-  TORCH_CHECK(vn.scalar_type() == qkvg.scalar_type() && out.scalar_type() == qkvg.scalar_type() && cu.scalar_type() == at::kInt);
+  TORCH_CHECK(vshare >= 1 && G % vshare == 0);
+  TORCH_CHECK(qkvg.size(1) >= H * d + G * d + (gate ? G / vshare * dv + H : 0) && vn.size(0) == T && vn.size(1) >= G / vshare * dv && out.numel() == T * H * dv);
+  TORCH_CHECK(vn.scalar_type() == qkvg.scalar_type() && cu.scalar_type() == at::kInt);
   c10::cuda::CUDAGuard g(qkvg.device());
   const int rc = rb_sink_window_prefill(qkvg.data_ptr(), qkvg.stride(0), vn.data_ptr(), out.data_ptr(), same_type_ptr(temp, qkvg, H, "temp"),
                                         same_type_ptr(sink, qkvg, H, "sink"), cu.data_ptr<int>(), (int)cu.numel() - 1, (int)max_seqlen, (int)H, (int)G,
-                                        (int)d, (int)dv, (float)scale, (int)window, (int)keep, (float)slope_base, gate ? 1 : 0, dt_code(qkvg), cur_stream());
+                                        (int)d, (int)dv, (float)scale, (int)window, (int)keep, (float)slope_base, gate ? 1 : 0, dt_code(qkvg), (int)vshare,
+                                        vn.stride(0), dt_code(out), cur_stream());
   TORCH_CHECK(rc == 0, "sink_window_attention: unsupported shape (rc ", rc, ")");
 }
 
@@ -149,16 +155,19 @@ void sink_window_attention_tc(const Tensor& qkvg, const Tensor& vn, Tensor out, 
 
 void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& temp, const OptT& sink, Tensor kc, Tensor vc, const Tensor& lens,
                                   const OptT& slots, int64_t H, int64_t G, int64_t d, int64_t dv, double scale, int64_t window, int64_t keep,
-                                  double slope_base, bool gate, bool do_norm, double eps) {
+                                  double slope_base, bool gate, bool do_norm, double eps, int64_t vshare) {
   CHECK_ROWS(qkvg); CHECK_IN(out); CHECK_IN(kc); CHECK_IN(vc); CHECK_IN(lens);
   const int64_t B = qkvg.size(0);
-  TORCH_CHECK(qkvg.size(1) >= H * d + G * (d + dv) + (gate ? H : 0) && out.numel() == B * H * dv && lens.scalar_type() == at::kInt);
-  TORCH_CHECK(kc.dim() == 4 && kc.size(1) == G && kc.size(3) == d && vc.size(1) == G && vc.size(3) == dv && vc.size(2) == kc.size(2));
-  TORCH_CHECK(kc.scalar_type() == qkvg.scalar_type() && vc.scalar_type() == qkvg.scalar_type() && out.scalar_type() == qkvg.scalar_type());
+  TORCH_CHECK(vshare >= 1 && G % vshare == 0);
+  const int64_t Gv = G / vshare;
+  TORCH_CHECK(qkvg.size(1) >= H * d + G * d + Gv * dv + (gate ? H : 0) && out.numel() == B * H * dv && lens.scalar_type() == at::kInt);
+  TORCH_CHECK(kc.dim() == 4 && kc.size(1) == G && kc.size(3) == d && vc.size(1) == Gv && vc.size(3) == dv && vc.size(2) == kc.size(2));
+  TORCH_CHECK(kc.scalar_type() == qkvg.scalar_type() && vc.scalar_type() == qkvg.scalar_type());
+  TORCH_CHECK(out.scalar_type() == qkvg.scalar_type() || out.scalar_type() == at::kFloat);
   TORCH_CHECK(slots.has_value() || kc.size(0) >= B);
   c10::cuda::CUDAGuard g(qkvg.device());
   const int rep = (int)(H / G);
-  if (qkvg.scalar_type() != at::kFloat && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
+  if (qkvg.scalar_type() != at::kFloat && vshare == 1 && out.scalar_type() == qkvg.scalar_type() && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
       qkvg.stride(0) % 8 == 0 && (H * d) % 8 == 0 && reinterpret_cast<uintptr_t>(qkvg.data_ptr()) % 16 == 0) {
     // enough CTAs for two per SM, at least 128 keys per split (the cache's row count bounds the visible keys).  Measured at 32 rows x
     // 4 kv heads x 576 keys with a cold L2: 65 us with 3 splits + merge, 74 us as one split
@@ -181,7 +190,7 @@ void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& te
   const int rc = rb_sink_window_decode(qkvg.data_ptr(), qkvg.stride(0), out.data_ptr(), same_type_ptr(temp, qkvg, H, "temp"),
                                        same_type_ptr(sink, qkvg, H, "sink"), kc.data_ptr(), vc.data_ptr(), lens.data_ptr<int>(), int_ptr(slots, B, "slots"),
                                        (int)B, (int)H, (int)G, (int)d, (int)dv, (int)kc.size(2), (float)scale, (int)window, (int)keep, (float)slope_base,
-                                       gate ? 1 : 0, do_norm ? 1 : 0, (float)eps, dt_code(qkvg), cur_stream());
+                                       gate ? 1 : 0, do_norm ? 1 : 0, (float)eps, dt_code(qkvg), (int)vshare, dt_code(out), cur_stream());
   TORCH_CHECK(rc == 0, "sink_window_decode_attention: unsupported shape (rc ", rc, ")");
 }
 
@@ -254,11 +263,11 @@ void register_state_ops(torch::Library& m) {
   m.def("embed_sinusoid(Tensor ids, Tensor wte, Tensor pos, Tensor? slots, Tensor inv_freq, Tensor(a!) out) -> ()", &embed_sinusoid);
   m.def("concat_cast(Tensor a, Tensor b, Tensor(a!) out) -> ()", &concat_cast);
   m.def("relu2(Tensor x) -> Tensor", &relu2);
-  m.def("rms_norm_rows(Tensor(a!) x, Tensor? y, Tensor w, Tensor(b!) out, float eps) -> ()", &rms_norm_rows);
-  m.def("value_norm_store(Tensor qkvg, Tensor(a!) vout, Tensor(b!)? kc, Tensor(c!)? vc, Tensor? tok_slot, Tensor pos, Tensor? remain, int H, int G, int d, int dv, int keep, bool do_norm, float eps) -> ()", &value_norm_store);
-  m.def("sink_window_attention(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate) -> ()", &sink_window_attention);
+  m.def("rms_norm_rows(Tensor(a!) x, Tensor? y, Tensor w, Tensor(b!) out, float eps, float w_offset=0.0) -> ()", &rms_norm_rows);
+  m.def("value_norm_store(Tensor qkvg, Tensor(a!) vout, Tensor(b!)? kc, Tensor(c!)? vc, Tensor? tok_slot, Tensor pos, Tensor? remain, int H, int G, int d, int dv, int keep, bool do_norm, float eps, int vshare=1) -> ()", &value_norm_store);
+  m.def("sink_window_attention(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate, int vshare=1) -> ()", &sink_window_attention);
   m.def("sink_window_attention_tc(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, float scale, int window, int keep, float slope_base, bool gate) -> ()", &sink_window_attention_tc);
-  m.def("sink_window_decode_attention(Tensor qkvg, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor(b!) kc, Tensor(c!) vc, Tensor lens, Tensor? slots, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate, bool do_norm, float eps) -> ()", &sink_window_decode_attention);
+  m.def("sink_window_decode_attention(Tensor qkvg, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor(b!) kc, Tensor(c!) vc, Tensor lens, Tensor? slots, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate, bool do_norm, float eps, int vshare=1) -> ()", &sink_window_decode_attention);
   m.def("delta_prepare(Tensor proj, Tensor conv_w, Tensor A_log, Tensor dt_bias, Tensor(a!) u, Tensor? pos, Tensor(b!)? conv_state, Tensor? tok_slot, Tensor? remain, Tensor? slots, int H, int G, int d, int dv, int taps, float unit_eps) -> ()", &delta_prepare);
   m.def("delta_rule_scan(Tensor u, Tensor(a!) o, Tensor cu, Tensor(b!)? s_state, Tensor? slots, int H, int G, int d, int dv) -> ()", &delta_rule_scan);
   m.def("delta_rule_step(Tensor u, Tensor(a!) o, Tensor(b!) s_state, Tensor? slots, int H, int G, int d, int dv) -> ()", &delta_rule_step);

@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
                                                                  const int* __restrict__ cache_lens, const int* __restrict__ slots,
                                                                  float* __restrict__ out, float* __restrict__ part_acc,
                                                                  float* __restrict__ part_ml, int B, int H, int rank, int R, int window,
-                                                                 int splits) {
+                                                                 int splits, const float* __restrict__ sink) {
   extern __shared__ float sm[];
   const int RP = ((rank + 3) & ~3) + 4;        // padded row: 16-byte aligned, rows 4 banks apart
   float* qs = sm;                              // [kHT][RP]
@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
 #pragma unroll
     for (int h = 0; h < kHT; ++h) {
       if (h >= nh) break;
-      const float inv = 1.f / al[h];
+      // a sink logit is one more term of the denominator: no key, no value
+      const float inv = 1.f / (al[h] + (sink != nullptr ? expf(sink[h0 + h] - ps[h]) : 0.f));
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         if (r0 + i < rank) out[((int64_t)(h0 + h) * B + b) * rank + r0 + i] = acc[h][i] * inv;
@@ -439,7 +440,7 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
 
 // out[h, b, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a split without keys has m = -inf, l = 0.
 __global__ void __launch_bounds__(128) latent_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                                                    float* __restrict__ out, int rank, int splits) {
+                                                                    float* __restrict__ out, int rank, int splits, const float* __restrict__ sink, int B) {
   const int64_t row = blockIdx.x;      // (h, b)
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(row * splits + s) * 2]);
@@ -448,6 +449,7 @@ __global__ void __launch_bounds__(128) latent_decode_combine_kernel(const float*
     const float m = part_ml[(row * splits + s) * 2];
     if (m != -INFINITY) L += part_ml[(row * splits + s) * 2 + 1] * expf(m - M);
   }
+  if (sink != nullptr) L += expf(sink[row / B] - M);
   for (int r = threadIdx.x; r < rank; r += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < splits; ++s) {
@@ -527,9 +529,9 @@ int rb_latent_append(const void* qc, int64_t ldq, int n_q, const void* w, void* 
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-// qa, out: [H, B, rank] fp32.  part_acc [H, B, splits, rank], part_ml [H, B, splits, 2] (splits > 1).
+// qa, out: [H, B, rank] fp32; sink [H] fp32 or null (a bare logit in every head's softmax denominator).  part_acc [H, B, splits, rank], part_ml [H, B, splits, 2] (splits > 1).
 int rb_latent_decode_core(const float* qa, const void* cache, const int* cache_lens, const int* slots, float* out, float* part_acc,
-                          float* part_ml, int B, int H, int rank, int R, int window, int splits, int dt, cudaStream_t s) {
+                          float* part_ml, int B, int H, int rank, int R, int window, int splits, int dt, const float* sink, cudaStream_t s) {
   if (B == 0) return 0;
   if (rank > kMaxRank || splits < 1 || (splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return 1;
   const int RP = ((rank + 3) & ~3) + 4;
@@ -539,11 +541,11 @@ int rb_latent_decode_core(const float* qa, const void* cache, const int* cache_l
   RB_DISPATCH_T(dt, {
     auto kern = latent_decode_core_kernel<T>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
-    kern<<<grid, kCT, smem, s>>>(qa, (const T*)cache, cache_lens, slots, out, part_acc, part_ml, B, H, rank, R, window, splits);
+    kern<<<grid, kCT, smem, s>>>(qa, (const T*)cache, cache_lens, slots, out, part_acc, part_ml, B, H, rank, R, window, splits, sink);
   });
   if (cudaGetLastError() != cudaSuccess) return 2;
   if (splits > 1) {
-    latent_decode_combine_kernel<<<(unsigned)(H * B), 128, 0, s>>>(part_acc, part_ml, out, rank, splits);
+    latent_decode_combine_kernel<<<(unsigned)(H * B), 128, 0, s>>>(part_acc, part_ml, out, rank, splits, sink, B);
     if (cudaGetLastError() != cudaSuccess) return 2;
   }
   return 0;

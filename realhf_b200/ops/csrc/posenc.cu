@@ -3,7 +3,7 @@
 //                    in fp32 from the fp32 table f (rounded once from float64 on the host)
 //   concat_cast      [a | b] along the last dim into one tensor of another type (the input of a projection reading two streams)
 //   relu2            relu(x)^2
-//   rms_norm_rows    out = x / sqrt(mean(x^2) + eps) * w per row (fp32 statistics, any storage types); with a branch output y it
+//   rms_norm_rows    out = x / sqrt(mean(x^2) + eps) * (w + w_off) per row (fp32 statistics, any storage types); with a branch output y it
 //                    first forms x <- x + y in place (fp32 sum stored in x's type): the residual add fused into the next norm
 #include "anytype.cuh"
 
@@ -57,7 +57,8 @@ __global__ void relu2_kernel(const void* __restrict__ x, void* __restrict__ out,
 
 // one CTA per row; the row is read once from DRAM (second pass from L1 / L2)
 __global__ void __launch_bounds__(256) rms_norm_rows_kernel(void* __restrict__ x, int dtx, const void* __restrict__ y, int dty,
-                                                            const void* __restrict__ w, int dtw, void* __restrict__ out, int dto, int W, float eps) {
+                                                            const void* __restrict__ w, int dtw, void* __restrict__ out, int dto, int W, float eps,
+                                                            float w_off) {
   __shared__ float red[32];
   const int64_t base = (int64_t)blockIdx.x * W;
   const bool vec = (W & 3) == 0;
@@ -88,19 +89,19 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(void* __restrict__ x
   if (vec) {
     for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
       const float4 v = rb::ld4_any(x, dtx, base + i), g = rb::ld4_any(w, dtw, i);
-      rb::st4_any(out, dto, base + i, make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w));
+      rb::st4_any(out, dto, base + i, make_float4(v.x * r * (g.x + w_off), v.y * r * (g.y + w_off), v.z * r * (g.z + w_off), v.w * r * (g.w + w_off)));
     }
   } else {
-    for (int i = threadIdx.x; i < W; i += blockDim.x) rb::st_any(out, dto, base + i, rb::ld_any(x, dtx, base + i) * r * rb::ld_any(w, dtw, i));
+    for (int i = threadIdx.x; i < W; i += blockDim.x) rb::st_any(out, dto, base + i, rb::ld_any(x, dtx, base + i) * r * (rb::ld_any(w, dtw, i) + w_off));
   }
 }
 
 }  // namespace
 
 extern "C" int rb_rms_norm_rows(void* x, int dtx, const void* y, int dty, const void* w, int dtw, void* out, int dto, int64_t rows, int W, float eps,
-                                cudaStream_t s) {
+                                float w_off, cudaStream_t s) {
   if (rows == 0) return 0;
-  return rb::launch_pdl(rms_norm_rows_kernel, dim3((unsigned)rows), dim3(256), 0, s, x, dtx, y, dty, w, dtw, out, dto, W, eps) == cudaSuccess ? 0 : -3;
+  return rb::launch_pdl(rms_norm_rows_kernel, dim3((unsigned)rows), dim3(256), 0, s, x, dtx, y, dty, w, dtw, out, dto, W, eps, w_off) == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int rb_embed_sinusoid(const int64_t* ids, const void* wte, int dtw, const int* pos, const int* slots, const float* inv_freq, float* out,

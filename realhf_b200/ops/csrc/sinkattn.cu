@@ -7,12 +7,16 @@
 //
 // Everything is fp32 arithmetic whatever the storage type (a type code per launch: 0 fp32, 1 bf16, 2 fp16); exact expf (compiled
 // without fast-math).  The projection output `qkvg` [T, ld] holds [q (H x d) | k (G x d) | v (G x dv) | gate logits] per row.
-// Caches: kc [n_slots, G, rows, d], vc [n_slots, G, rows, dv]; position p lives in row p when p < keep_first, else in row
-// keep_first + (p - keep_first) % (rows - keep_first).
+// Caches: kc [n_slots, G, rows, d], vc [n_slots, G / vshare, rows, dv]; position p lives in row p when p < keep_first, else in row
+// keep_first + (p - keep_first) % (rows - keep_first).  `vshare` consecutive key heads read the same value head (1: a value head
+// per key head; 2: the two score maps of differential attention over one set of values), and the projection row then holds
+// G / vshare value heads.
 //
 //   value_norm_store       packed prefill: vhat -> [T, G * dv], and the rows a later decode step can still see -> caches
 //   sink_window_prefill    packed prefill over the batch's own keys: CTA = 32 queries x 1 head of one sequence, 32-key tiles in
 //                          shared memory, online softmax whose running maximum starts at the sink (denominator 1)
+//   qk_head_norm           in place: every query / key head of a row divided by its root mean square, times a weight per section
+//   diff_combine           differential attention: o = a1 - lambda a2 per head, o / sqrt(mean(o^2) + eps) * (1 - diff)
 //   sink_window_decode     one token per row: CTA = (row, kv head) serving the group's query heads; appends k / vhat, then walks the
 //                          visible cache rows in 128-key tiles (one key per thread for the scores, one column per thread for P.V)
 #include "anytype.cuh"
@@ -32,7 +36,7 @@ RB_DEVICE int cache_row(int p, int keep, int rows) {
 __global__ void __launch_bounds__(128) value_norm_store_kernel(const void* __restrict__ qkvg, int64_t ld, int dt, void* __restrict__ vout,
                                                                 void* __restrict__ kc, void* __restrict__ vc, const int* __restrict__ tok_slot,
                                                                 const int* __restrict__ pos, const int* __restrict__ remain, int H, int G, int d,
-                                                                int dv, int keep, int rows, int do_norm, float eps) {
+                                                                int dv, int keep, int rows, int do_norm, float eps, int vshare) {
   const int64_t t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int64_t base = t * ld;
@@ -44,20 +48,24 @@ __global__ void __launch_bounds__(128) value_norm_store_kernel(const void* __res
     if (slot >= 0 && !(p < keep || remain[t] < rows - keep)) slot = -1;   // a row that a later position of this prompt overwrites
     row = cache_row(p, keep, rows);
   }
-  for (int g = warp; g < G; g += nwarp) {
+  const int Gv = G / vshare;
+  for (int g = warp; g < Gv; g += nwarp) {
     float ss = 0.f;
     for (int c = lane; c < dv; c += 32) { const float v = ld_any(qkvg, dt, base + ov + g * dv + c); ss += v * v; }
     ss = rb::warp_sum(ss);
     const float r = do_norm ? 1.f / sqrtf(ss / (float)dv + eps) : 1.f;
-    const int64_t crow = slot >= 0 ? ((int64_t)slot * G + g) * rows + row : 0;
+    const int64_t crow = slot >= 0 ? ((int64_t)slot * Gv + g) * rows + row : 0;
     for (int c = lane; c < dv; c += 32) {
       const float v = ld_any(qkvg, dt, base + ov + g * dv + c) * r;
-      st_any(vout, dt, t * (int64_t)(G * dv) + g * dv + c, v);
+      st_any(vout, dt, t * (int64_t)(Gv * dv) + g * dv + c, v);
       if (slot >= 0) st_any(vc, dt, crow * dv + c, v);
     }
-    if (slot >= 0)
-      for (int c = lane; c < d; c += 32) st_any(kc, dt, crow * d + c, ld_any(qkvg, dt, base + ok + g * d + c));
   }
+  if (slot >= 0)
+    for (int g = warp; g < G; g += nwarp) {
+      const int64_t crow = ((int64_t)slot * G + g) * rows + row;
+      for (int c = lane; c < d; c += 32) st_any(kc, dt, crow * d + c, ld_any(qkvg, dt, base + ok + g * d + c));
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ packed prefill
@@ -65,12 +73,13 @@ constexpr int BQ = 32, BK = 32, kPfThreads = 128;
 
 struct PrefillParams {
   const void* qkvg; int64_t ld;
-  const void* vn;            // [T, G * dv]
-  void* out;                 // [T, H * dv]
+  const void* vn;            // [T, vld] rows of G / vshare value heads
+  void* out;                 // [T, H * dv] in type dto
   const void* temp; const void* sink;   // [H] in the model type, or null
   const int* cu;             // [n_seqs + 1]
   int H, G, d, dv, window, keep, gate, dt;
   float scale, slope_base;
+  int vshare, dto; int64_t vld;
 };
 
 // NJ = ceil(dv / 32): a thread owns 2 query rows x NJ float4 column groups of the output tile
@@ -125,7 +134,7 @@ __global__ void __launch_bounds__(kPfThreads) sink_window_prefill_kernel(Prefill
     }
     for (int idx = tid; idx < BK * dvp; idx += kPfThreads) {
       const int r = idx / dvp, e = idx % dvp;
-      Vs[r * vs + e] = (k0 + r < kend && e < dv) ? ld_any(p.vn, dt, (int64_t)(s0 + k0 + r) * (p.G * dv) + g * dv + e) : 0.f;
+      Vs[r * vs + e] = (k0 + r < kend && e < dv) ? ld_any(p.vn, dt, (int64_t)(s0 + k0 + r) * p.vld + (g / p.vshare) * dv + e) : 0.f;
     }
     __syncthreads();
     // scores of 2 rows x 4 keys
@@ -185,7 +194,7 @@ __global__ void __launch_bounds__(kPfThreads) sink_window_prefill_kernel(Prefill
       }
     }
   }
-  const int og = p.H * d + p.G * d + p.G * dv;
+  const int og = p.H * d + p.G * d + p.G / p.vshare * dv;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int i = q0 + ty * 2 + r;
@@ -198,9 +207,48 @@ __global__ void __launch_bounds__(kPfThreads) sink_window_prefill_kernel(Prefill
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int col = j * 32 + tx * 4 + c;
-        if (col < dv) st_any(p.out, dt, t * (int64_t)(p.H * dv) + h * dv + col, o[r][j][c] * f);
+        if (col < dv) st_any(p.out, p.dto, t * (int64_t)(p.H * dv) + h * dv + col, o[r][j][c] * f);
       }
   }
+}
+
+// ------------------------------------------------------------------------------------------------ query / key head norm, differential combine
+// a warp per (row, head); heads [0, nq) take weight wq, heads [nq, nq + nk) weight wk; the heads are consecutive in the row
+__global__ void __launch_bounds__(128) qk_head_norm_kernel(void* __restrict__ x, int64_t ld, int dt, const void* __restrict__ wq,
+                                                           const void* __restrict__ wk, int64_t n_rows, int nq, int nk, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  if (id >= n_rows * (nq + nk)) return;
+  const int64_t t = id / (nq + nk);
+  const int h = (int)(id % (nq + nk));
+  const void* w = h < nq ? wq : wk;
+  const int64_t base = t * ld + (int64_t)h * d;
+  float ss = 0.f;
+  for (int c = lane; c < d; c += 32) { const float v = ld_any(x, dt, base + c); ss += v * v; }
+  ss = rb::warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)d + eps);
+  for (int c = lane; c < d; c += 32) st_any(x, dt, base + c, ld_any(x, dt, base + c) * r * ld_any(w, dt, c));
+}
+
+// a [T, G, 2, per, dv] (the attention outputs of both maps, query heads grouped by key head), out [T, H * dv], H = G * per
+__global__ void __launch_bounds__(128) diff_combine_kernel(const void* __restrict__ a, int dta, const float* __restrict__ lam, void* __restrict__ out,
+                                                           int dto, int64_t n_rows, int H, int G, int dv, float diff, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  if (id >= n_rows * H) return;
+  const int64_t t = id / H;
+  const int h = (int)(id % H), per = H / G, g = h / per, hh = h % per;
+  const int64_t b1 = (t * 2 * H + (int64_t)(g * 2) * per + hh) * dv, b2 = b1 + (int64_t)per * dv;
+  const float l = lam[0];
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) { const float o = ld_any(a, dta, b1 + c) - l * ld_any(a, dta, b2 + c); ss += o * o; }
+  ss = rb::warp_sum(ss);
+  const float r = (1.f - diff) / sqrtf(ss / (float)dv + eps);
+  for (int c = lane; c < dv; c += 32) st_any(out, dto, id * dv + c, (ld_any(a, dta, b1 + c) - l * ld_any(a, dta, b2 + c)) * r);
 }
 
 // ------------------------------------------------------------------------------------------------ decode
@@ -213,6 +261,7 @@ struct DecodeParams {
   const int* lens; const int* slots;
   int H, G, d, dv, rows, window, keep, gate, do_norm, dt;
   float scale, slope_base, eps;
+  int vshare, dto;
 };
 
 __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeParams p) {
@@ -229,8 +278,9 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
   const int slot = p.slots ? p.slots[b] : b;
   const int n = p.lens[slot];               // the new token's position
   const int64_t base = (int64_t)b * p.ld;
-  const int ok = p.H * d, ov = ok + p.G * d, og = ov + p.G * dv;
-  const int64_t cbase = ((int64_t)slot * p.G + g) * p.rows;
+  const int gv = g / p.vshare, Gv = p.G / p.vshare;
+  const int ok = p.H * d, ov = ok + p.G * d, og = ov + Gv * dv;
+  const int64_t cbase = ((int64_t)slot * p.G + g) * p.rows, vbase = ((int64_t)slot * Gv + gv) * p.rows;
 
   for (int idx = tid; idx < rep * d; idx += kDecThreads) {
     const int h = h0 + idx / d;
@@ -239,11 +289,12 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
   // append the new key and normalised value (fp32 statistics; the stored value is what later steps read)
   {
     float ss = 0.f;
-    for (int c = tid; c < dv; c += kDecThreads) { const float v = ld_any(p.qkvg, dt, base + ov + g * dv + c); vnew[c] = v; ss += v * v; }
+    for (int c = tid; c < dv; c += kDecThreads) { const float v = ld_any(p.qkvg, dt, base + ov + gv * dv + c); vnew[c] = v; ss += v * v; }
     ss = rb::block_reduce<false>(ss, red);
     const float r = p.do_norm ? 1.f / sqrtf(ss / (float)dv + p.eps) : 1.f;
-    const int64_t row = cbase + cache_row(n, p.keep, p.rows);
-    for (int c = tid; c < dv; c += kDecThreads) st_any(p.vc, dt, row * dv + c, vnew[c] * r);
+    const int nr = cache_row(n, p.keep, p.rows);
+    const int64_t row = cbase + nr, vrow_new = vbase + nr;   // (CTAs that share a value head write the same values)
+    for (int c = tid; c < dv; c += kDecThreads) st_any(p.vc, dt, vrow_new * dv + c, vnew[c] * r);
     for (int c = tid; c < d; c += kDecThreads) st_any(p.kc, dt, row * d + c, ld_any(p.qkvg, dt, base + ok + g * d + c));
   }
   __syncthreads();   // the CTA's own global writes are visible to its threads from here on
@@ -323,7 +374,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
         l[r] += sum;
       }
     for (int k = 0; k < cnt; ++k) {
-      const int64_t vrow = (cbase + rws[k]) * dv;
+      const int64_t vrow = (vbase + rws[k]) * dv;
 #pragma unroll
       for (int c = 0; c < kMaxColsPerThread; ++c) {
         const int col = tid + c * kDecThreads;
@@ -346,7 +397,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
 #pragma unroll
       for (int c = 0; c < kMaxColsPerThread; ++c) {
         const int col = tid + c * kDecThreads;
-        if (col < dv) st_any(p.out, dt, (int64_t)b * (p.H * dv) + h * dv + col, acc[r][c] * f);
+        if (col < dv) st_any(p.out, p.dto, (int64_t)b * (p.H * dv) + h * dv + col, acc[r][c] * f);
       }
     }
 }
@@ -587,18 +638,19 @@ int launch_fast(const FastParams& fp, int B, cudaStream_t s) {
 
 extern "C" int rb_value_norm_store(const void* qkvg, int64_t ld, int dt, void* vout, void* kc, void* vc, const int* tok_slot, const int* pos,
                                    const int* remain, int64_t T, int H, int G, int d, int dv, int keep, int rows, int do_norm, float eps,
-                                   cudaStream_t s) {
+                                   int vshare, cudaStream_t s) {
   if (T == 0) return 0;
-  value_norm_store_kernel<<<(unsigned)T, 128, 0, s>>>(qkvg, ld, dt, vout, kc, vc, tok_slot, pos, remain, H, G, d, dv, keep, rows, do_norm, eps);
+  if (vshare < 1 || G % vshare) return -1;
+  value_norm_store_kernel<<<(unsigned)T, 128, 0, s>>>(qkvg, ld, dt, vout, kc, vc, tok_slot, pos, remain, H, G, d, dv, keep, rows, do_norm, eps, vshare);
   return 0;
 }
 
 extern "C" int rb_sink_window_prefill(const void* qkvg, int64_t ld, const void* vn, void* out, const void* temp, const void* sink, const int* cu,
                                       int n_seqs, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base,
-                                      int gate, int dt, cudaStream_t s) {
+                                      int gate, int dt, int vshare, int64_t vld, int dto, cudaStream_t s) {
   if (n_seqs == 0 || max_seqlen == 0) return 0;
-  if (dv > 256 || d > 512 || H % G) return -1;
-  PrefillParams p{qkvg, ld, vn, out, temp, sink, cu, H, G, d, dv, window, keep, gate, dt, scale, slope_base};
+  if (dv > 256 || d > 512 || H % G || vshare < 1 || G % vshare) return -1;
+  PrefillParams p{qkvg, ld, vn, out, temp, sink, cu, H, G, d, dv, window, keep, gate, dt, scale, slope_base, vshare, dto, vld};
   const int nj = dv <= 32 ? 1 : dv <= 64 ? 2 : dv <= 128 ? 4 : 8;
   const int dp = (d + 3) & ~3;
   const size_t smem = sizeof(float) * ((size_t)(BQ + BK) * (dp + 4) + (size_t)BK * (nj * 32 + 4) + (size_t)BQ * (BK + 1));
@@ -620,11 +672,11 @@ extern "C" int rb_sink_window_prefill(const void* qkvg, int64_t ld, const void* 
 
 extern "C" int rb_sink_window_decode(const void* qkvg, int64_t ld, void* out, const void* temp, const void* sink, void* kc, void* vc,
                                      const int* lens, const int* slots, int B, int H, int G, int d, int dv, int rows, float scale, int window,
-                                     int keep, float slope_base, int gate, int do_norm, float eps, int dt, cudaStream_t s) {
+                                     int keep, float slope_base, int gate, int do_norm, float eps, int dt, int vshare, int dto, cudaStream_t s) {
   if (B == 0) return 0;
   const int rep = min(H / G, kMaxRep);
-  if (H % G || dv > kDecThreads * kMaxColsPerThread) return -1;
-  DecodeParams p{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, dv, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps};
+  if (H % G || dv > kDecThreads * kMaxColsPerThread || vshare < 1 || G % vshare) return -1;
+  DecodeParams p{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, dv, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps, vshare, dto};
   const size_t smem = sizeof(float) * ((size_t)rep * d + (size_t)rep * kDecThreads + rep * 5 + 32 + dv + kDecThreads);
   if (smem > 48 * 1024) cudaFuncSetAttribute(sink_window_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   sink_window_decode_kernel<<<dim3(B, G, RB_CEIL_DIV(H / G, kMaxRep)), kDecThreads, smem, s>>>(p);
@@ -640,8 +692,23 @@ extern "C" int rb_sink_window_decode_fast(const void* qkvg, int64_t ld, void* ou
   if (B == 0) return 0;
   if ((dt != 1 && dt != 2) || (d != 64 && d != 128) || H % G || ld % 8 || ((uintptr_t)qkvg & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15))
     return -1;
-  FastParams fp{DecodeParams{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, d, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps},
+  FastParams fp{DecodeParams{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, d, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps, 1, dt},
                 part_acc, part_ml, splits};
   if (dt == 1) return d == 128 ? launch_fast<__nv_bfloat16, 128>(fp, B, s) : launch_fast<__nv_bfloat16, 64>(fp, B, s);
   return d == 128 ? launch_fast<__half, 128>(fp, B, s) : launch_fast<__half, 64>(fp, B, s);
+}
+
+extern "C" int rb_qk_head_norm(void* x, int64_t ld, int dt, const void* wq, const void* wk, int64_t T, int nq, int nk, int d, float eps,
+                               cudaStream_t s) {
+  const int64_t n = T * (nq + nk);
+  if (n == 0) return 0;
+  return rb::launch_pdl(qk_head_norm_kernel, dim3((unsigned)RB_CEIL_DIV(n, (int64_t)4)), dim3(128), 0, s, x, ld, dt, wq, wk, T, nq, nk, d, eps) == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int rb_diff_combine(const void* a, int dta, const float* lam, void* out, int dto, int64_t T, int H, int G, int dv, float diff, float eps,
+                               cudaStream_t s) {
+  const int64_t n = T * H;
+  if (n == 0) return 0;
+  if (H % G) return -1;
+  return rb::launch_pdl(diff_combine_kernel, dim3((unsigned)RB_CEIL_DIV(n, (int64_t)4)), dim3(128), 0, s, a, dta, lam, out, dto, T, H, G, dv, diff, eps) == cudaSuccess ? 0 : 2;
 }

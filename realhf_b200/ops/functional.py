@@ -593,12 +593,12 @@ def set_intervals(src: torch.Tensor, dst: torch.Tensor, intervals: List[Tuple[in
 _DT_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 
-def group_rmsnorm_ref(x, w, groups: int, eps: float):
-    """fp32 [.., W]: x cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times w."""
+def group_rmsnorm_ref(x, w, groups: int, eps: float, w_offset: float = 0.0):
+    """fp32 [.., W]: x cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times (w + w_offset)."""
     shp = x.shape
     p = x.float().reshape(*shp[:-1], groups, shp[-1] // groups)
     p = p * torch.rsqrt(p.pow(2).mean(-1, keepdim=True) + eps)
-    return p.reshape(shp) * w.float()
+    return p.reshape(shp) * (w.float() + w_offset)
 
 
 def cached_on(t: torch.Tensor, name: str, build):
@@ -637,16 +637,20 @@ def sublayer_input_ref(x, w, groups, eps, conv_w, pos, out_dtype, state=None, to
     return h.to(out_dtype)
 
 
-def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=None, tok_slot=None, remain=None):
+def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=None, tok_slot=None, remain=None, w_offset: float = 0.0):
     """What a sublayer of a packed batch reads: n = grouped RMSNorm(x) * w, then h_t = n_t + sum_j conv_w[:, j] * n_(t - taps + 1 + j)
     over the tokens of the same sequence (zeros before its start; `pos` [T] int32 = position inside the sequence).  conv_w None:
     h = n.  With `state` [n_slots, taps - 1, W] fp32, the n of the last taps - 1 tokens of every sequence is left in
     state[tok_slot[t]] (oldest first; rows of a shorter sequence are not written, the slot manager zeroes them), `remain[t]`
-    being the number of tokens that follow t in its sequence."""
+    being the number of tokens that follow t in its sequence.  `w_offset` (weights stored around zero: the factor is w + 1) is a
+    feature of the plain form (one group, no convolution)."""
     if use_native(x) and groups == 1 and conv_w is None:     # a plain RMSNorm: one CTA per row
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        lib().rms_norm_rows(x.contiguous(), None, w, out, eps)
+        lib().rms_norm_rows(x.contiguous(), None, w, out, eps, w_offset)
         return out
+    if w_offset:
+        assert groups == 1 and conv_w is None, "a weight offset needs the plain norm"
+        return group_rmsnorm_ref(x, w, 1, eps, w_offset).to(out_dtype)
     if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:   # the kernels hold <= 8 taps
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input(x.contiguous(), w, _tap_major(conv_w), pos, out, state if conv_w is not None else None,
@@ -668,13 +672,16 @@ def sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype):
     return h.to(out_dtype)
 
 
-def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out_dtype):
+def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out_dtype, w_offset: float = 0.0):
     """Decode form of `sublayer_input` (one token per row): the earlier inputs come from state[slots[b]] ([taps - 1, W] fp32,
     oldest first), which is then shifted by one with this token's n appended.  slots None = row b uses slot b."""
     if use_native(x) and groups == 1 and conv_w is None:
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        lib().rms_norm_rows(x.contiguous(), None, w, out, eps)
+        lib().rms_norm_rows(x.contiguous(), None, w, out, eps, w_offset)
         return out
+    if w_offset:
+        assert groups == 1 and conv_w is None, "a weight offset needs the plain norm"
+        return group_rmsnorm_ref(x, w, 1, eps, w_offset).to(out_dtype)
     if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input_step(x.contiguous(), w, _tap_major(conv_w), out, state if conv_w is not None else None, slots, groups, eps)
@@ -759,15 +766,15 @@ def embed_sinusoid(ids, wte, pos, base: float = 10000.0, slots=None):
     return embed_sinusoid_ref(ids, wte, pos if slots is None else pos[slots.long()], inv_freq[1])
 
 
-def add_rms_norm_(x, y, w, eps: float, out_dtype):
-    """x <- x + y in place (fp32 sum, stored in x's dtype), then RMSNorm(x) * w in out_dtype: the residual add of one sublayer fused
-    into the norm of the next."""
+def add_rms_norm_(x, y, w, eps: float, out_dtype, w_offset: float = 0.0):
+    """x <- x + y in place (fp32 sum, stored in x's dtype), then RMSNorm(x) * (w + w_offset) in out_dtype: the residual add of one
+    sublayer fused into the norm of the next."""
     if use_native(x) and x.is_contiguous():
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        lib().rms_norm_rows(x, y.contiguous(), w, out, eps)
+        lib().rms_norm_rows(x, y.contiguous(), w, out, eps, w_offset)
         return out
     x.copy_((x.float() + y.float()).to(x.dtype))
-    return group_rmsnorm_ref(x, w, 1, eps).to(out_dtype)
+    return group_rmsnorm_ref(x, w, 1, eps, w_offset).to(out_dtype)
 
 
 def relu2(x):

@@ -171,3 +171,96 @@ def gated_head_norm(o, w, gate, eps: float, out_dtype):
         lib().gated_head_norm(o, w, gate, out, eps)
         return out
     return gated_head_norm_ref(o, w, gate, eps, out_dtype)
+
+
+# ------------------------------------------------------------------------------------------------ matrix-memory LSTM
+# (`MLSTMConfig`).  The fused projection output `proj` [T, ld] = [q (H x d) | k (H x d) | v (H x dv) | output gate (H x dv) | input
+# gate logits (H) | forget gate logits (H) | padding]; `gate_bias` [2H] = the two gates' biases.  Per head, all fp32:
+#   i = cap tanh((x_i + b_i) / cap),  f = logsigmoid(cap tanh((x_f + b_f) / cap)),  m' = max(f + m, i)   (m starts at 0)
+#   S <- exp(f + m - m') S + exp(i - m') k v^T,   n likewise with k alone,   o = S^T (q d^-1/2) / (max(|n . q d^-1/2|, exp(-m')) + 1e-6)
+# n is stored as column dv of the state, so `state` is [n_slots, H, d, dv + 1] and `m_state` [n_slots, H].  `mlstm_scan` returns
+# the raw rows [S^T q | n . q] and m per token; `mlstm_out` applies the denominator, the per-head RMS norm (no weight), the
+# full-width weight and the sigmoid output gate.
+
+
+def _mlstm_offsets(c):
+    nq, nv = c.n_heads * c.qk_dim, c.n_heads * c.v_dim
+    return nq, 2 * nq, 2 * nq + nv, 2 * nq + 2 * nv        # k, v, output gate, gate logits
+
+
+def _mlstm_ref(proj, gate_bias, c, seqs, state, m_state, slot_of, load_state):
+    T = proj.shape[0]
+    H, d, dv, cap = c.n_heads, c.qk_dim, c.v_dim, float(c.gate_cap)
+    ok, ov, _, oif = _mlstm_offsets(c)
+    q = proj[:, :ok].float().view(T, H, d) * (d ** -0.5)
+    k = proj[:, ok:ov].float().view(T, H, d)
+    v = torch.cat([proj[:, ov:ov + H * dv].float().view(T, H, dv), torch.ones(T, H, 1, device=proj.device)], -1)
+    b = gate_bias.float()
+    ig = cap * torch.tanh((proj[:, oif:oif + H].float() + b[:H]) / cap)
+    fg = F.logsigmoid(cap * torch.tanh((proj[:, oif + H:oif + 2 * H].float() + b[H:]) / cap))
+    o = torch.empty(T, H, dv + 1, dtype=torch.float32, device=proj.device)
+    mo = torch.empty(T, H, dtype=torch.float32, device=proj.device)
+    for n, (s0, e0) in enumerate(seqs):
+        if e0 == s0:
+            continue
+        sl = slot_of(n)
+        if load_state:
+            S, m = state[sl].clone(), m_state[sl].clone()
+        else:
+            S = torch.zeros(H, d, dv + 1, dtype=torch.float32, device=proj.device)
+            m = torch.zeros(H, dtype=torch.float32, device=proj.device)
+        for t in range(s0, e0):
+            mn = torch.maximum(fg[t] + m, ig[t])
+            dec, inp = torch.exp(fg[t] + m - mn), torch.exp(ig[t] - mn)
+            S = dec[:, None, None] * S + (inp[:, None] * k[t])[:, :, None] * v[t][:, None, :]
+            m = mn
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+            mo[t] = m
+        if state is not None:
+            state[sl] = S
+            m_state[sl] = m
+    return o, mo
+
+
+def mlstm_scan(proj, gate_bias, c, cu_seqlens, state=None, m_state=None, seq_slot=None, load_state: bool = False):
+    """Packed recurrence over every sequence, from zero (or, with `load_state`, from the slot's state); the final state is left in
+    state[seq_slot[n]] when `state` is given.  Returns (o [T, H, dv + 1] fp32, m [T, H] fp32)."""
+    T = proj.shape[0]
+    H, d, dv = c.n_heads, c.qk_dim, c.v_dim
+    if use_native(proj) and d <= 1024:
+        o = torch.empty(T, H, dv + 1, dtype=torch.float32, device=proj.device)
+        mo = torch.empty(T, H, dtype=torch.float32, device=proj.device)
+        lib().mlstm_scan(proj, gate_bias, o, mo, cu_seqlens, state, m_state, seq_slot if state is not None else None, H, d, dv,
+                         float(c.gate_cap), bool(load_state))
+        return o, mo
+    cu = cu_seqlens.tolist()
+    return _mlstm_ref(proj, gate_bias, c, list(zip(cu[:-1], cu[1:])), state, m_state,
+                      lambda n: int(seq_slot[n]) if seq_slot is not None else n, load_state)
+
+
+def mlstm_step(proj, gate_bias, c, state, m_state, slots=None):
+    """One token per row against state[slots[b]] (slots None: row b is slot b), updated in place.  Returns (o, m) as `mlstm_scan`."""
+    B = proj.shape[0]
+    H, d, dv = c.n_heads, c.qk_dim, c.v_dim
+    if use_native(proj) and d <= 1024:
+        o = torch.empty(B, H, dv + 1, dtype=torch.float32, device=proj.device)
+        mo = torch.empty(B, H, dtype=torch.float32, device=proj.device)
+        lib().mlstm_scan(proj, gate_bias, o, mo, None, state, m_state, slots, H, d, dv, float(c.gate_cap), True)
+        return o, mo
+    return _mlstm_ref(proj, gate_bias, c, [(b, b + 1) for b in range(B)], state, m_state,
+                      lambda n: int(slots[n]) if slots is not None else n, True)
+
+
+def mlstm_out(o, m, w, gate, eps: float, out_dtype):
+    """o [T, H, dv + 1] fp32 raw rows, m [T, H]: h = o[..., :dv] / (max(|o[..., dv]|, exp(-m)) + 1e-6); h / rms(h) per head; times
+    w [H * dv] and sigmoid(gate [T, >= H * dv]) -> [T, H * dv] in out_dtype."""
+    T, H, dvx = o.shape
+    dv = dvx - 1
+    if use_native(o):
+        out = torch.empty(T, H * dv, dtype=out_dtype, device=o.device)
+        lib().mlstm_out(o, m, w, gate, out, eps)
+        return out
+    den = torch.maximum(o[..., dv].abs(), torch.exp(-m)) + 1e-6
+    h = o[..., :dv] / den.unsqueeze(-1)
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    return (h.reshape(T, H * dv) * w.float() * torch.sigmoid(gate[:, : H * dv].float())).to(out_dtype)
