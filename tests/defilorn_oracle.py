@@ -188,3 +188,80 @@ def forward(cfg: dict, sd: Dict[str, torch.Tensor], tokens: List[int]) -> Tuple[
         trace.append(x.clone())
     h = rms(x, eps) * (1.0 + sd["final.norm"].to(F64))
     return lin(sd["head"], h), trace
+
+
+# ------------------------------------------------------------------------------------------------ helpers of the tests
+
+
+def tensor_shapes(cfg: dict) -> Dict[str, Tuple[int, ...]]:
+    """Name -> shape of every tensor of a checkpoint with this config."""
+    W, V = int(cfg["width"]), int(cfg["vocab"])
+    out: Dict[str, Tuple[int, ...]] = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    for i, lay in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lay["mixer"]
+        out[p + "norm1"] = (W,)
+        if lay["type"] == "latent_attention":
+            H, d, r, dv, kr, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out.update({p + "mix.dq": (qr, W), p + "mix.dq.norm": (qr,), p + "mix.uq": (H * (d + r), qr), p + "mix.dkv": (kr + r, W),
+                        p + "mix.dkv.norm": (kr,), p + "mix.uk": (H * d, kr), p + "mix.uv": (H * dv, kr), p + "mix.sink": (H,),
+                        p + "mix.g": (H * dv, W), p + "mix.o": (W, H * dv)})
+        elif lay["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * 2 * d, W), p + "mix.k": (G * 2 * d, W), p + "mix.v": (G * dv, W), p + "mix.q.norm": (d,),
+                        p + "mix.k.norm": (d,), p + "mix.lq1": (d,), p + "mix.lk1": (d,), p + "mix.lq2": (d,), p + "mix.lk2": (d,),
+                        p + "mix.o": (W, H * dv)})
+        else:
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * d, W), p + "mix.k": (H * d, W), p + "mix.v": (H * dv, W), p + "mix.g": (H * dv, W),
+                        p + "mix.o": (W, H * dv), p + "mix.norm": (H * dv,), p + "mix.i": (H, W), p + "mix.i.b": (H,), p + "mix.f": (H, W),
+                        p + "mix.f.b": (H,)})
+        f = lay.get("mlp")
+        if not f:
+            continue
+        out[p + "norm2"] = (W,)
+        if f["kind"] == "dense":
+            out.update({p + "mlp.gate": (f["ff"], W), p + "mlp.up": (f["ff"], W), p + "mlp.down": (W, f["ff"])})
+        else:
+            E, I, F = f["router"]["experts"], f["router"].get("identity", 0), f["expert"]["ff"]
+            for e in range(E):
+                out.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+            out.update({p + "mlp.router": (E + I, W), p + "mlp.correction": (E + I,)})
+            if f.get("shared"):
+                Fs = f["shared"]["ff"]
+                out.update({p + "mlp.shared.gate": (Fs, W), p + "mlp.shared.up": (Fs, W), p + "mlp.shared.down": (W, Fs), p + "mlp.shared.sg": (1, W)})
+    return out
+
+
+def random_checkpoint(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
+    """Random weights, every value exactly representable in bfloat16 (so that both serving types read the same numbers)."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if name.endswith(("norm1", "norm2", "final.norm")) or name.endswith(".norm") and len(shape) == 1:
+            t = 0.2 * torch.randn(shape, generator=g) + (1.0 if name.endswith(("q.norm", "k.norm", "dq.norm", "dkv.norm", "mix.norm")) else 0.0)
+        elif last == "sink":
+            t = torch.randn(shape, generator=g)
+        elif last == "correction":
+            t = 0.05 * torch.randn(shape, generator=g)
+        elif name.endswith("i.b"):
+            t = torch.randn(shape, generator=g)
+        elif name.endswith("f.b"):
+            t = 2.0 + torch.randn(shape, generator=g)
+        elif last in ("lq1", "lk1", "lq2", "lk2"):
+            t = 0.4 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * (1.3 / math.sqrt(shape[-1]))
+        sd[name] = t.bfloat16().float()
+    return sd
+
+
+def greedy(cfg: dict, sd: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(cfg, sd, seq)[0][-1].argmax())
+        out.append(nxt)
+        seq.append(nxt)
+    return out
