@@ -1,6 +1,6 @@
 """Prefill / decode throughput of a heterogeneous-stack design next to the closest homogeneous model of equal size, and the
-roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra` or
-`--serve-bench tizodra` (the default workload of bench.py is unaffected).
+roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra`,
+`--serve-bench tizodra` or `--serve-bench defilorn` (the default workload of bench.py is unaffected).
 
 Both models run through `models.generation`: prefill = `prefill_into_state` (the packed prefill `generate` performs) into a
 standing decode state, decode = the CUDA-graph loop of `generate` with the sampler in the graph; random weights, bf16.  Timing: CUDA events, >= 3 warm-up calls, weights + state far larger than L2 per call for
@@ -53,11 +53,37 @@ def tizodra_config(s: dict, n_layers: int = 4) -> dict:
                 norm=dict(eps=1e-5), vocab=s["vocab"], width=s["width"])
 
 
+DEFILORN_SIZES = {
+    # name: width, heads, kv heads (differential attention), head sizes (attention: two maps of `dim` per head), window, latent ranks,
+    # unrotated / rotated query-key dims of the latent attention, dense ff, experts, expert ff, top, identity experts, shared ff, vocab
+    "1b-like": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, kv_rank=512, q_rank=768, nope=64, rot=64, ff=8192,
+                    experts=8, eff=2048, top=2, identity=1, sff=2048, vocab=32000),
+    "7b-like": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, kv_rank=512, q_rank=1536, nope=64, rot=64, ff=11008,
+                    experts=8, eff=2816, top=2, identity=1, sff=2816, vocab=32000),
+}
+
+
+def defilorn_config(s: dict, n_layers: int = 4) -> dict:
+    """Differential attention, matrix-memory LSTM, rotated latent attention in turn; dense and mixture-of-experts feed-forwards alternate."""
+    dense = dict(kind="dense", ff=s["ff"])
+    moe = dict(kind="moe", expert=dict(ff=s["eff"]), router=dict(experts=s["experts"], identity=s["identity"], top=s["top"]), shared=dict(ff=s["sff"]))
+    att = dict(type="attention", mixer=dict(diff=0.6, dim=s["dim"], heads=s["heads"], kv_heads=s["kv_heads"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+                                            mask=dict(size=s["window"])))
+    mls = dict(type="mlstm", mixer=dict(dim=s["dim"], gate_cap=15.0, heads=s["heads"], vdim=s["vdim"]))
+    lat = dict(type="latent_attention", mixer=dict(dim=s["nope"], heads=s["heads"], kv_rank=s["kv_rank"], q_rank=s["q_rank"], rot_dim=s["rot"],
+                                                   vdim=s["vdim"], scale=(s["nope"] + s["rot"]) ** -0.5,
+                                                   rot=dict(base=1e6, dims=s["rot"], scaling=dict(factor=8.0, fast=32.0, original=2048, slow=1.0))))
+    kinds = [att, mls, lat]
+    layers = [dict(kinds[i % 3], mlp=moe if i % 2 else dense) for i in range(n_layers)]
+    return dict(architecture="Defilorn", layers=layers, loop=dict(start=0, stop=min(2, n_layers), times=1), norm=dict(eps=1e-5), vocab=s["vocab"],
+                width=s["width"])
+
+
 def _models(s: dict, n_layers: int, dev, design: str = "rapodra"):
     from realhf_b200.api.model import ReaLModelConfig
     from realhf_b200.models import hf_io
     from realhf_b200.models.real_model import ReaLModel
-    cfg = rapodra_config(s, n_layers) if design == "rapodra" else tizodra_config(s, n_layers)
+    cfg = {"rapodra": rapodra_config, "tizodra": tizodra_config, "defilorn": defilorn_config}[design](s, n_layers)
     rc = hf_io.family(design).config_from_dict(cfg, False)
     new = ReaLModel(rc, dtype=torch.bfloat16, device=dev).init_random_fast()
     lc = ReaLModelConfig(n_layers=n_layers, n_kv_heads=s.get("kv_heads", s["heads"]), n_q_heads=s["heads"], hidden_dim=s["width"], intermediate_dim=s["ff"],
@@ -309,8 +335,136 @@ def tizodra_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx:
     return rows
 
 
+def defilorn_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx: int, dev, peaks: Dict[str, float]) -> List[dict]:
+    """The Defilorn kernels next to the like kernels of the framework's other models at the same token count and head sizes: LLaMA's
+    attention and row kernels, Tizodra's delta rule for the matrix-memory LSTM.  Attention FLOPs count the visible (query, key) pairs;
+    the fp32 recurrences are held against the nominal fp32 CUDA-core rate or their bytes, whichever is slower."""
+    from realhf_b200.api.model import DeltaRuleConfig
+    from realhf_b200.models import hf_io
+    from realhf_b200.models.hetero_block import packed_meta
+    from realhf_b200.ops import attention as A
+    from realhf_b200.ops import functional as OF
+    from realhf_b200.ops import recurrent as RC
+    bf = torch.bfloat16
+    rc = hf_io.family("defilorn").config_from_dict(defilorn_config(s, 3), False)
+    wa, ml, la = rc.blocks[0].wattn, rc.blocks[1].mlstm, rc.blocks[2].attn
+    W, H, G, d, dv, win, FF = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], s["ff"]
+    T = batch * prompt_len
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_tflops = 148 * 128 * 2 * 1.9e9 / 1e12
+    rows = []
+
+    def add(kernel, like, ms, nbytes, flops, simt_fp32=False):
+        peak = fp32_tflops if simt_fp32 else peaks["bf16_tflops"]
+        floor_ms = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peak * 1e12)) * 1e3
+        rows.append(dict(bench="kernel", size=name, kernel=kernel, like=like, ms=round(ms, 4), gbytes=round(nbytes / 1e9, 4),
+                         gflop=round(flops / 1e9, 2), roofline_ms=round(floor_ms, 4), frac_of_measured_roofline=round(floor_ms / ms, 4),
+                         flop_peak="fp32 CUDA cores (nominal)" if simt_fp32 else "bf16 tensor (measured)"))
+
+    cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
+    slots = torch.arange(batch, dtype=torch.int32, device=dev)
+    meta = packed_meta(cu, T, slots, None, prompt_len)
+    x32 = torch.randn(T, W, device=dev)
+    xb = x32.to(bf)
+    w = torch.zeros(W, device=dev, dtype=bf)
+    # ---- row-wise
+    add("add_rms_norm_ (fp32 stream += branch, norm with 1 + w, prefill)", False, _time(lambda: OF.add_rms_norm_(x32, xb, w, 1e-5, bf, 1.0), 10, flush=flush),
+        T * W * 12, 0)
+    add("add_rmsnorm (llama, prefill)", True, _time(lambda: OF.add_rmsnorm(xb, xb, w, 1e-5), 10, flush=flush), T * W * 8, 0)
+    gu = torch.randn(T, 2 * FF, device=dev).to(bf)
+    add("gated_act gelu_tanh (prefill, stand-alone; the prefill path has it in the GEMM epilogue)", False, _time(lambda: OF.gated_act(gu, "gelu_tanh"), 10, flush=flush), T * FF * 6, 0)
+    add("gated_act silu (llama, prefill)", True, _time(lambda: OF.gated_act(gu, "silu"), 10, flush=flush), T * FF * 6, 0)
+    # ---- differential window attention
+    ld = 2 * H * d + 2 * G * d + G * dv
+    qkv = torch.randn(T, ld, device=dev).to(bf)
+    wn = torch.ones(d, device=dev, dtype=bf)
+    lamw = (torch.randn(4, d, device=dev) * 0.1).to(bf)
+    rows_c = wa.cache_rows(prompt_len + 64)
+    kc = torch.zeros(batch, 2 * G, rows_c, d, device=dev, dtype=bf)
+    vc = torch.zeros(batch, G, rows_c, dv, device=dev, dtype=bf)
+    from realhf_b200.ops import lib
+    add("qk_head_norm_ (prefill)", False, _time(lambda: lib().qk_head_norm_(qkv, wn, wn, 2 * H, 2 * G, d, 1e-5), 10, flush=flush), T * (2 * H + 2 * G) * d * 4, 0)
+    pairs = batch * sum(min(p + 1, win) for p in range(prompt_len))
+    add("diff_window_attention (prefill: norms + cache fill + both maps + combine)", False,
+        _time(lambda: A.diff_window_attention(qkv, wa, wn, wn, lamw, 1e-5, kc, vc, meta.tok_slot, meta.pos, meta.remain, cu, prompt_len), 3, warmup=1, flush=flush),
+        T * (ld + H * dv) * 2, 2.0 * pairs * 2 * H * (d + dv))
+    qkv_l = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    full_pairs = batch * prompt_len * (prompt_len + 1) // 2
+    add("varlen attention tcgen05 (llama, prefill, full causal)", True,
+        _time(lambda: A.varlen_attention_qkv(qkv_l, cu, prompt_len, H, G, d, None, True), 5, flush=flush), T * (2 * H + 2 * G) * d * 2, 4.0 * full_pairs * H * d)
+    keys = min(ctx + 1, win)
+    rows_d = wa.cache_rows(ctx + 64)
+    kc = torch.randn(batch, 2 * G, rows_d, d, device=dev).to(bf)
+    vc = torch.randn(batch, G, rows_d, dv, device=dev).to(bf)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    q1 = torch.randn(batch, ld, device=dev).to(bf)
+    add(f"diff_window_decode_attention (ctx {ctx}, {keys} keys, both maps)", False,
+        _time(lambda: A.diff_window_decode_attention(q1, wa, wn, wn, lamw, 1e-5, kc, vc, lens, None), 10, flush=flush),
+        batch * keys * G * (2 * d + dv) * 2, 2.0 * batch * 2 * H * keys * (d + dv))
+    kl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    vl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    qkv1 = torch.randn(batch, (H + 2 * G) * d, device=dev).to(bf)
+    cos, sin = OF.rope_tables(ctx + 64, d, 10000.0, dev)
+    add(f"decode_attention (llama, ctx {ctx}, all {ctx + 1} keys)", True,
+        _time(lambda: A.decode_attention(qkv1, kl, vl, lens, H, G, d, None, cos, sin), 10, flush=flush),
+        batch * (ctx + 1) * G * d * 2 * 2, 4.0 * batch * H * (ctx + 1) * d)
+    # ---- rotated latent attention
+    r, rot, dn, qr = la.kv_rank, la.rot_dim, la.qk_dim, la.q_rank
+    dq = dn + rot
+    proj = torch.randn(T, qr + r + rot + H * dv, device=dev).to(bf)
+    wq, wc = torch.ones(qr, device=dev, dtype=bf), torch.ones(r, device=dev, dtype=bf)
+    cache = torch.zeros(batch, prompt_len + 64, r + rot, device=dev, dtype=bf)
+    add("latent_rope_prepare (prefill: two norms + rotation + cache fill)", False,
+        _time(lambda: A.latent_rope_prepare(proj, la, wq, wc, 1e-5, meta.pos, cache, meta.tok_slot, meta.remain), 10, flush=flush),
+        T * (qr + r + rot) * 2 * 2 + T * (r + rot) * 2, 0)
+    cq, latent = A.latent_rope_prepare(proj, la, wq, wc, 1e-5, meta.pos, cache, meta.tok_slot, meta.remain)
+    q = torch.randn(T, H * dq, device=dev).to(bf)
+    kv = torch.randn(T, H * (dn + dv), device=dev).to(bf)
+    sink = torch.zeros(H, device=dev, dtype=bf)
+    add("latent_rope_attention (prefill: rotate + assemble + causal attention with a sink)", False,
+        _time(lambda: A.latent_rope_attention(q, kv, latent, la, sink, meta.pos, cu, prompt_len), 3, warmup=1, flush=flush),
+        T * H * (dq + dn + 2 * dv) * 2 + T * 2 * H * dq * 2 * 2, 2.0 * full_pairs * H * (dq + dv))
+    o = torch.randn(T, H * dv, device=dev).to(bf)
+    add("sigmoid_gate_ (prefill)", False, _time(lambda: A.sigmoid_gate_(o, proj[:, qr + r + rot:]), 10, flush=flush), T * H * dv * 6, 0)
+    cache = torch.randn(batch, ctx + 64, r + rot, device=dev).to(bf)
+    w_ukv = (torch.randn(H * (dn + dv), r, device=dev) * r ** -0.5).to(bf)
+    q1l = torch.randn(batch, H * dq, device=dev).to(bf)
+    add(f"latent_rope_decode_attention (ctx {ctx}, all {ctx + 1} keys)", False,
+        _time(lambda: A.latent_rope_decode_attention(q1l, la, w_ukv, sink, cache, lens, None), 10, flush=flush),
+        batch * (ctx + 1) * (r + rot) * 2 + H * (dn + dv) * r * 4, 2.0 * batch * H * ((ctx + 1) * (2 * r + rot) + (dn + dv) * r))
+    # ---- matrix-memory LSTM next to the delta rule
+    ldm = 2 * H * d + 2 * H * dv + (2 * H + 7) // 8 * 8
+    pm = (torch.randn(T, ldm, device=dev) * 0.5).to(bf)
+    gb = torch.zeros(2 * H, device=dev, dtype=bf)
+    S = torch.zeros(batch, H, d, dv + 1, device=dev)
+    M = torch.zeros(batch, H, device=dev)
+    add("mlstm_scan (prefill, fp32 recurrence)", False, _time(lambda: RC.mlstm_scan(pm, gb, ml, cu, S, M, slots), 3, warmup=1, flush=flush),
+        T * (2 * H * d + H * dv) * 2 + T * H * (dv + 2) * 4, T * H * 6.0 * d * (dv + 1), simt_fp32=True)
+    dl = DeltaRuleConfig(n_heads=H, n_kv_heads=H, qk_dim=d, v_dim=dv, conv_taps=1)
+    u = torch.randn(T, dl.conv_channels + 2 * H, device=dev) * 0.1
+    u[:, -2 * H:] = 0.5
+    s_state = torch.zeros(batch, H, d, dv, device=dev)
+    add("delta_rule_scan (tizodra, prefill, fp32 recurrence)", True, _time(lambda: RC.delta_rule_scan(u, dl, cu, s_state, slots), 3, warmup=1, flush=flush),
+        T * (dl.conv_channels + 2 * H + H * dv) * 4, T * H * 8.0 * d * dv, simt_fp32=True)
+    om, mm = RC.mlstm_scan(pm, gb, ml, cu, S, M, slots)
+    wo = torch.ones(H * dv, device=dev, dtype=bf)
+    add("mlstm_out (prefill: denominator + head norm + weight + gate)", False,
+        _time(lambda: RC.mlstm_out(om, mm, wo, pm[:, 2 * H * d + H * dv:], 1e-5, bf), 10, flush=flush), T * H * dv * 8, 0)
+    od = torch.randn(T, H, dv, device=dev)
+    add("gated_head_norm (tizodra, prefill)", True,
+        _time(lambda: RC.gated_head_norm(od, torch.ones(dv, device=dev, dtype=bf), pm[:, 2 * H * d + H * dv:2 * H * d + 2 * H * dv], 1e-5, bf), 10, flush=flush),
+        T * H * dv * 8, 0)
+    p1 = (torch.randn(batch, ldm, device=dev) * 0.5).to(bf)
+    add("mlstm_step (decode: state read + write)", False, _time(lambda: RC.mlstm_step(p1, gb, ml, S, M, None), 10, flush=flush),
+        batch * H * d * (dv + 1) * 8, batch * H * 6.0 * d * (dv + 1), simt_fp32=True)
+    u1 = torch.randn(batch, dl.conv_channels + 2 * H, device=dev) * 0.1
+    add("delta_rule_step (tizodra, decode: state read + write)", True, _time(lambda: RC.delta_rule_step(u1, dl, s_state, None), 10, flush=flush),
+        batch * H * d * dv * 8, batch * H * 8.0 * d * dv, simt_fp32=True)
+    return rows
+
+
 def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
-    assert design in ("rapodra", "tizodra")
+    assert design in ("rapodra", "tizodra", "defilorn")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     peaks = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
@@ -321,11 +475,11 @@ def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
         if "hbm_gbs" in d and "bf16_tflops" in d:
             peaks = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
     results = [dict(bench="peaks", **peaks)]
-    table = SIZES if design == "rapodra" else TIZODRA_SIZES
+    table = {"rapodra": SIZES, "tizodra": TIZODRA_SIZES, "defilorn": DEFILORN_SIZES}[design]
     for name in sizes or list(table):
         s = table[name]
         results += model_numbers(name, s, n_layers, batch=32, prompt_len=1024, new_tokens=33, dev=dev, design=design)
-        kn = kernel_numbers if design == "rapodra" else tizodra_kernel_numbers
+        kn = {"rapodra": kernel_numbers, "tizodra": tizodra_kernel_numbers, "defilorn": defilorn_kernel_numbers}[design]
         results += kn(name, s, batch=32, prompt_len=1024, ctx=2048, dev=dev, peaks=peaks)
     for r in results:
         print(json.dumps(r), flush=True)

@@ -562,10 +562,15 @@ def diff_window_attention(qkv, a, wq, wk, w_lambda, eps: float, k_cache, v_cache
         v_n = torch.empty(T, G * dv, dtype=qkv.dtype, device=qkv.device)
         lib().value_norm_store(qkv, v_n, k_cache, v_cache, tok_slot if k_cache is not None else None, pos,
                                remain if k_cache is not None else None, 2 * H, 2 * G, d, dv, a.keep_first, False, eps, 2)
-        att = torch.empty(T, 2 * H * dv, dtype=torch.float32, device=qkv.device)
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-        lib().sink_window_attention(qkv, v_n, att, None, None, cu_seqlens, max_seqlen, 2 * H, 2 * G, d, dv, a.scale, win, a.keep_first, -1.0, False, 2)
+        if _sink_tc_ok(qkv, v_n, av):
+            # 16-bit operands, head size 64 / 128: the tcgen05 kernel; both maps' weighted sums come back in the operand type
+            att = torch.empty(T, 2 * H * dv, dtype=qkv.dtype, device=qkv.device)
+            lib().sink_window_attention_tc(qkv, v_n, att, None, None, cu_seqlens, max_seqlen, 2 * H, 2 * G, d, a.scale, win, a.keep_first, -1.0, False, 2)
+        else:
+            att = torch.empty(T, 2 * H * dv, dtype=torch.float32, device=qkv.device)
+            lib().sink_window_attention(qkv, v_n, att, None, None, cu_seqlens, max_seqlen, 2 * H, 2 * G, d, dv, a.scale, win, a.keep_first, -1.0, False, 2)
         out = torch.empty(T, H * dv, dtype=qkv.dtype, device=qkv.device)
         lib().diff_combine(att, lam, out, H, G, dv, a.diff, eps)
         return out
@@ -608,7 +613,8 @@ def diff_window_decode_attention(qkv, a, wq, wk, w_lambda, eps: float, k_cache, 
     lam = diff_lambda(w_lambda, a.diff)
     if use_native(qkv) and dv <= 256:
         lib().qk_head_norm_(qkv, wq, wk, 2 * H, 2 * G, d, eps)
-        att = torch.empty(B, 2 * H * dv, dtype=torch.float32, device=qkv.device)
+        fast = qkv.dtype != torch.float32 and d == dv and d in (64, 128) and (H // G) in (1, 2, 4, 8)    # the streaming 16-bit kernel
+        att = torch.empty(B, 2 * H * dv, dtype=qkv.dtype if fast else torch.float32, device=qkv.device)
         lib().sink_window_decode_attention(qkv, att, None, None, k_cache, v_cache, cache_lens, slots, 2 * H, 2 * G, d, dv, a.scale,
                                            a.window if a.window is not None else -1, a.keep_first, -1.0, False, False, eps, 2)
         out = torch.empty(B, H * dv, dtype=qkv.dtype, device=qkv.device)
@@ -717,7 +723,12 @@ def latent_rope_attention(q, kv, lat, a, sink, pos, cu_seqlens, max_seqlen=None)
         out = torch.empty(T, H * dv, dtype=q.dtype, device=q.device)
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-        lib().sink_window_attention(qk, kv[:, H * d:], out, None, sink, cu_seqlens, max_seqlen, H, H, dq, dv, a.scale, -1, 0, -1.0, False, 1)
+        vv = kv[:, H * d:]
+        if (os.environ.get("REAL_WINDOW_ATTN", "tcgen05") == "tcgen05" and q.dtype in (torch.bfloat16, torch.float16) and dq == dv and dq in (64, 128)
+                and kv.stride(0) % 8 == 0 and (H * d) % 8 == 0 and vv.data_ptr() % 16 == 0):
+            lib().sink_window_attention_tc(qk, vv, out, None, sink, cu_seqlens, max_seqlen, H, H, dq, a.scale, -1, 0, -1.0, False, 1)
+        else:
+            lib().sink_window_attention(qk, vv, out, None, sink, cu_seqlens, max_seqlen, H, H, dq, dv, a.scale, -1, 0, -1.0, False, 1)
         return out
     qh = q.float().view(T, H, dq)
     if rot:

@@ -55,6 +55,7 @@ struct AttnParams {
   const void* gate;       // gate logits, element (t, h) at gate[t * gate_ld + h], or null
   int64_t gate_ld;
   float slope_base;       // < 0: no distance term
+  int vshare = 1;         // consecutive key heads that read one value head (V has nkv / vshare heads)
 };
 
 template <int kD> struct ACfg {
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
           for (int kb = 0; kb < C::kDBlocks; ++kb)
             ptx::tma_load_2d(sV + st * C::kKVBytes + half * (64 * kD * 2) + kb * (64 * 128), &tma_v, bar(V_FULL + st),
-                             hk * kD + kb * 64, row + half * 64);
+                             (hk / p.vshare) * kD + kb * 64, row + half * 64);
       }
     }
   } else if (warp == 1) {
@@ -401,19 +402,19 @@ extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* ou
 extern "C" int rb_attn_fwd_sink(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens, int64_t q_ld, int64_t k_ld,
                                 int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd, int max_seqlen, float scale, int window,
                                 int keep, const void* temp, const void* sink, const void* gate, int64_t gate_ld, float slope_base, int dt,
-                                cudaStream_t s) {
+                                int vshare, cudaStream_t s) {
   if (hd != 128 && hd != 64) return -1;
   if (dt != 1 && dt != 2) return -2;
-  if (nq % nkv != 0 || T <= 0 || B <= 0 || max_seqlen <= 0) return -3;
+  if (nq % nkv != 0 || T <= 0 || B <= 0 || max_seqlen <= 0 || vshare < 1 || nkv % vshare) return -3;
   if ((q_ld | k_ld | v_ld | out_ld) % 8 != 0) return -4;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return -5;
   CUtensorMap mq, mk, mv;
   const int bf = dt == 1;
   if (!make_tmap(&mq, q, bf, T, (uint64_t)nq * hd, q_ld, 64, kBQ)) return -10;
   if (!make_tmap(&mk, k, bf, T, (uint64_t)nkv * hd, k_ld, 64, kBKV)) return -11;
-  if (!make_tmap(&mv, v, bf, T, (uint64_t)nkv * hd, v_ld, 64, 64)) return -12;
+  if (!make_tmap(&mv, v, bf, T, (uint64_t)(nkv / vshare) * hd, v_ld, 64, 64)) return -12;
   AttnParams p{cu_seqlens, out, nullptr, out_ld, T, nq, nkv, scale, 1, window > 0 ? window : 0, window > 0 ? keep : 0, temp, sink, gate, gate_ld,
-               slope_base};
+               slope_base, vshare};
   if (hd == 128) {
     return bf ? launch_attn_fwd<128, __nv_bfloat16, 1, true>(mq, mk, mv, p, B, max_seqlen, s)
               : launch_attn_fwd<128, __half, 0, true>(mq, mk, mv, p, B, max_seqlen, s);

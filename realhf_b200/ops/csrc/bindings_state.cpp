@@ -48,9 +48,9 @@ int rb_sink_window_prefill(const void*, int64_t, const void*, void*, const void*
 int rb_sink_window_decode(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, int, int, int, int, int, int,
                           float, int, int, float, int, int, float, int, int, int, cudaStream_t);
 int rb_sink_window_decode_fast(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, float*, float*, int, int,
-                               int, int, int, int, float, int, int, float, int, int, float, int, cudaStream_t);
+                               int, int, int, int, float, int, int, float, int, int, float, int, int, cudaStream_t);
 int rb_attn_fwd_sink(const void*, const void*, const void*, void*, const int*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, float,
-                     int, int, const void*, const void*, const void*, int64_t, float, int, cudaStream_t);
+                     int, int, const void*, const void*, const void*, int64_t, float, int, int, cudaStream_t);
 int rb_delta_prepare(const void*, int64_t, int, const void*, const void*, const void*, float*, const int*, float*, const int*, const int*, const int*,
                      int64_t, int, int, int, int, int, float, cudaStream_t);
 int rb_delta_rule(const float*, float*, const int*, float*, const int*, int, int, int, int, int, int, cudaStream_t);
@@ -138,18 +138,21 @@ void sink_window_attention(const Tensor& qkvg, const Tensor& vn, Tensor out, con
 
 // tensor-core form: 16-bit operands, equal query / value head size of 64 or 128
 void sink_window_attention_tc(const Tensor& qkvg, const Tensor& vn, Tensor out, const OptT& temp, const OptT& sink, const Tensor& cu, int64_t max_seqlen,
-                              int64_t H, int64_t G, int64_t d, double scale, int64_t window, int64_t keep, double slope_base, bool gate) {
-  CHECK_ROWS(qkvg); CHECK_IN(vn); CHECK_IN(out); CHECK_IN(cu);
+                              int64_t H, int64_t G, int64_t d, double scale, int64_t window, int64_t keep, double slope_base, bool gate,
+                              int64_t vshare) {
+  CHECK_ROWS(qkvg); CHECK_ROWS(vn); CHECK_IN(out); CHECK_IN(cu);
   const int64_t T = qkvg.size(0);
-  TORCH_CHECK(qkvg.size(1) >= H * d + 2 * G * d + (gate ? H : 0) && vn.numel() == T * G * d && out.numel() == T * H * d);
+  TORCH_CHECK(vshare >= 1 && G % vshare == 0);
+  TORCH_CHECK(qkvg.size(1) >= H * d + G * d + (gate ? G / vshare * d + H : 0) && vn.size(0) == T && vn.size(1) >= G / vshare * d && out.numel() == T * H * d);
   TORCH_CHECK(vn.scalar_type() == qkvg.scalar_type() && out.scalar_type() == qkvg.scalar_type() && cu.scalar_type() == at::kInt);
   c10::cuda::CUDAGuard g(qkvg.device());
   const char* base = static_cast<const char*>(qkvg.data_ptr());
   const int es = (int)qkvg.element_size();
-  const int rc = rb_attn_fwd_sink(base, base + H * d * es, vn.data_ptr(), out.data_ptr(), cu.data_ptr<int>(), qkvg.stride(0), qkvg.stride(0), G * d,
+  const int rc = rb_attn_fwd_sink(base, base + H * d * es, vn.data_ptr(), out.data_ptr(), cu.data_ptr<int>(), qkvg.stride(0), qkvg.stride(0), vn.stride(0),
                                   H * d, (int)T, (int)cu.numel() - 1, (int)H, (int)G, (int)d, (int)max_seqlen, (float)scale, (int)window, (int)keep,
                                   same_type_ptr(temp, qkvg, H, "temp"), same_type_ptr(sink, qkvg, H, "sink"),
-                                  gate ? base + (H * d + 2 * G * d) * es : nullptr, qkvg.stride(0), (float)slope_base, dt_code(qkvg), cur_stream());
+                                  gate ? base + (H * d + G * d + G / vshare * d) * es : nullptr, qkvg.stride(0), (float)slope_base, dt_code(qkvg),
+                                  (int)vshare, cur_stream());
   TORCH_CHECK(rc == 0, "sink_window_attention_tc: unsupported shape (rc ", rc, ")");
 }
 
@@ -167,7 +170,7 @@ void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& te
   TORCH_CHECK(slots.has_value() || kc.size(0) >= B);
   c10::cuda::CUDAGuard g(qkvg.device());
   const int rep = (int)(H / G);
-  if (qkvg.scalar_type() != at::kFloat && vshare == 1 && out.scalar_type() == qkvg.scalar_type() && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
+  if (qkvg.scalar_type() != at::kFloat && out.scalar_type() == qkvg.scalar_type() && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
       qkvg.stride(0) % 8 == 0 && (H * d) % 8 == 0 && reinterpret_cast<uintptr_t>(qkvg.data_ptr()) % 16 == 0) {
     // enough CTAs for two per SM, at least 128 keys per split (the cache's row count bounds the visible keys).  Measured at 32 rows x
     // 4 kv heads x 576 keys with a cold L2: 65 us with 3 splits + merge, 74 us as one split
@@ -184,7 +187,7 @@ void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& te
                                                int_ptr(slots, B, "slots"), splits > 1 ? pa.data_ptr<float>() : nullptr,
                                                splits > 1 ? pm.data_ptr<float>() : nullptr, splits, (int)B, (int)H, (int)G, (int)d, (int)rows, (float)scale,
                                                (int)window, (int)keep, (float)slope_base, gate ? 1 : 0, do_norm ? 1 : 0, (float)eps, dt_code(qkvg),
-                                               cur_stream());
+                                               (int)vshare, cur_stream());
     if (rcf == 0) return;
   }
   const int rc = rb_sink_window_decode(qkvg.data_ptr(), qkvg.stride(0), out.data_ptr(), same_type_ptr(temp, qkvg, H, "temp"),
@@ -266,7 +269,7 @@ void register_state_ops(torch::Library& m) {
   m.def("rms_norm_rows(Tensor(a!) x, Tensor? y, Tensor w, Tensor(b!) out, float eps, float w_offset=0.0) -> ()", &rms_norm_rows);
   m.def("value_norm_store(Tensor qkvg, Tensor(a!) vout, Tensor(b!)? kc, Tensor(c!)? vc, Tensor? tok_slot, Tensor pos, Tensor? remain, int H, int G, int d, int dv, int keep, bool do_norm, float eps, int vshare=1) -> ()", &value_norm_store);
   m.def("sink_window_attention(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate, int vshare=1) -> ()", &sink_window_attention);
-  m.def("sink_window_attention_tc(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, float scale, int window, int keep, float slope_base, bool gate) -> ()", &sink_window_attention_tc);
+  m.def("sink_window_attention_tc(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, float scale, int window, int keep, float slope_base, bool gate, int vshare=1) -> ()", &sink_window_attention_tc);
   m.def("sink_window_decode_attention(Tensor qkvg, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor(b!) kc, Tensor(c!) vc, Tensor lens, Tensor? slots, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate, bool do_norm, float eps, int vshare=1) -> ()", &sink_window_decode_attention);
   m.def("delta_prepare(Tensor proj, Tensor conv_w, Tensor A_log, Tensor dt_bias, Tensor(a!) u, Tensor? pos, Tensor(b!)? conv_state, Tensor? tok_slot, Tensor? remain, Tensor? slots, int H, int G, int d, int dv, int taps, float unit_eps) -> ()", &delta_prepare);
   m.def("delta_rule_scan(Tensor u, Tensor(a!) o, Tensor cu, Tensor(b!)? s_state, Tensor? slots, int H, int G, int d, int dv) -> ()", &delta_rule_scan);

@@ -442,9 +442,10 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
   const int slot = p.slots ? p.slots[b] : b;
   const int n = p.lens[slot];
   const T* row_in = reinterpret_cast<const T*>(p.qkvg) + (int64_t)b * p.ld;
-  const int ok = p.H * HD, ov = ok + p.G * HD, og = ov + p.G * HD;
+  const int Gv = p.G / p.vshare, gv = g / p.vshare;
+  const int ok = p.H * HD, ov = ok + p.G * HD, og = ov + Gv * HD;
   T* kc = reinterpret_cast<T*>(p.kc) + ((int64_t)slot * p.G + g) * p.rows * HD;
-  T* vc = reinterpret_cast<T*>(p.vc) + ((int64_t)slot * p.G + g) * p.rows * HD;
+  T* vc = reinterpret_cast<T*>(p.vc) + ((int64_t)slot * Gv + gv) * p.rows * HD;   // (CTAs that share a value head append the same values)
 
   float q[REP][8], slope[REP], kn[8], vn[8];
 #pragma unroll
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
     slope[r] = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(h + 1) / (float)p.H) : 0.f;
   }
   f_load8(row_in + ok + g * HD + sub * 8, kn);
-  f_load8(row_in + ov + g * HD + sub * 8, vn);
+  f_load8(row_in + ov + gv * HD + sub * 8, vn);
   if (p.do_norm) {
     float ss = 0.f;
 #pragma unroll
@@ -630,7 +631,7 @@ int launch_fast(const FastParams& fp, int B, cudaStream_t s) {
 #undef RB_L
   if (fp.splits > 1)
     rb::launch_pdl(sink_window_decode_merge_kernel<T, HD>, dim3(B * p.H), dim3(HD), 0, s, (const float*)fp.part_acc, (const float*)fp.part_ml,
-                   reinterpret_cast<const T*>(p.qkvg), p.ld, p.H * HD + 2 * p.G * HD, p.H, p.gate, reinterpret_cast<T*>(p.out), fp.splits);
+                   reinterpret_cast<const T*>(p.qkvg), p.ld, p.H * HD + p.G * HD + p.G / p.vshare * HD, p.H, p.gate, reinterpret_cast<T*>(p.out), fp.splits);
   return 0;
 }
 
@@ -688,11 +689,11 @@ extern "C" int rb_sink_window_decode(const void* qkvg, int64_t ld, void* out, co
 extern "C" int rb_sink_window_decode_fast(const void* qkvg, int64_t ld, void* out, const void* temp, const void* sink, void* kc, void* vc,
                                           const int* lens, const int* slots, float* part_acc, float* part_ml, int splits, int B, int H, int G, int d,
                                           int rows, float scale, int window, int keep, float slope_base, int gate, int do_norm, float eps, int dt,
-                                          cudaStream_t s) {
+                                          int vshare, cudaStream_t s) {
   if (B == 0) return 0;
-  if ((dt != 1 && dt != 2) || (d != 64 && d != 128) || H % G || ld % 8 || ((uintptr_t)qkvg & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15))
+  if ((dt != 1 && dt != 2) || (d != 64 && d != 128) || H % G || vshare < 1 || G % vshare || ld % 8 || ((uintptr_t)qkvg & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15))
     return -1;
-  FastParams fp{DecodeParams{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, d, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps, 1, dt},
+  FastParams fp{DecodeParams{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, d, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps, vshare, dt},
                 part_acc, part_ml, splits};
   if (dt == 1) return d == 128 ? launch_fast<__nv_bfloat16, 128>(fp, B, s) : launch_fast<__nv_bfloat16, 64>(fp, B, s);
   return d == 128 ? launch_fast<__half, 128>(fp, B, s) : launch_fast<__half, 64>(fp, B, s);

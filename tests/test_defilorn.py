@@ -182,6 +182,41 @@ def test_mechanism_alone_prompt_then_decoding(device, dtype, name):
     assert model_ok(errs, dtype), float(torch.cat(errs).max())
 
 
+TC_SHAPES = {
+    "diff-64-window150": lambda: one_layer(att(heads=4, kv_heads=2, dim=64, vdim=64, window=150), width=64),
+    "diff-128-window128": lambda: one_layer(att(heads=2, kv_heads=2, dim=128, vdim=128, window=128, diff=0.3), width=64),
+    "diff-64-nowindow-rep4": lambda: one_layer(att(heads=4, kv_heads=1, dim=64, vdim=64, window=None), width=64),
+    "latent-32+32-64": lambda: one_layer(lat(heads=3, dim=32, rot=32, vdim=64, kv_rank=48, q_rank=40, base=1e4), width=64),
+    "latent-64+64-128": lambda: one_layer(lat(heads=2, dim=64, rot=64, vdim=128, kv_rank=72, q_rank=64, base=1e6), width=64),
+}
+
+
+@pytest.mark.parametrize("device,dtype", [CPU, GPU32, GPU16])
+@pytest.mark.parametrize("name", list(TC_SHAPES))
+def test_head_shapes_of_the_tensor_core_and_streaming_kernels(device, dtype, name):
+    """Head sizes 64 / 128 with equal query and value size: in 16 bit the prompts run the tcgen05 kernel (two maps sharing a value
+    head, or the sink) and decoding the streaming kernel; sequences of 1, 130 and 300 tokens cross the 128-key tiles and the window."""
+    cfg = TC_SHAPES[name]()
+    w = O.random_checkpoint(cfg, 21)
+    m = build(cfg, w, device, dtype)
+    V = cfg["vocab"]
+    seqs = [toks(n, V, 20 + n) for n in (1, 130, 300)]
+    more = 6
+    full = [s + toks(more, V, 90 + len(s)) for s in seqs]
+    want = [O.forward(cfg, w, s)[0] for s in full]
+    sess = gen.StepSession(m, max_len=320, n_slots=3)
+    h = sess.prefill(list(enumerate(seqs)))
+    lg = sess.logits(h)
+    off, errs = 0, []
+    for s, wl in zip(seqs, want):
+        errs.append(row_errs(lg[off:off + len(s)], wl[:len(s)]))
+        off += len(s)
+    for k in range(more):
+        lg = sess.logits(sess.decode([(i, full[i][len(seqs[i]) + k]) for i in range(3)]))
+        errs += [row_errs(lg[i:i + 1], want[i][len(seqs[i]) + k][None]) for i in range(3)]
+    assert model_ok(errs, dtype), float(torch.cat(errs).max())
+
+
 # ------------------------------------------------------------------------------------------------ edges, made to show
 
 
