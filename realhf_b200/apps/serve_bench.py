@@ -56,9 +56,9 @@ def tizodra_config(s: dict, n_layers: int = 4) -> dict:
 DEFILORN_SIZES = {
     # name: width, heads, kv heads (differential attention), head sizes (attention: two maps of `dim` per head), window, latent ranks,
     # unrotated / rotated query-key dims of the latent attention, dense ff, experts, expert ff, top, identity experts, shared ff, vocab
-    "1b-like": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, kv_rank=512, q_rank=768, nope=64, rot=64, ff=8192,
+    "1b-like": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, kv_rank=448, q_rank=768, nope=64, rot=64, ff=8192,
                     experts=8, eff=2048, top=2, identity=1, sff=2048, vocab=32000),
-    "7b-like": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, kv_rank=512, q_rank=1536, nope=64, rot=64, ff=11008,
+    "7b-like": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, kv_rank=448, q_rank=1536, nope=64, rot=64, ff=11008,
                     experts=8, eff=2816, top=2, identity=1, sff=2816, vocab=32000),
 }
 

@@ -131,10 +131,19 @@ __global__ void __launch_bounds__(128) latent_query_rope_kernel(const void* __re
   }
 }
 
-__global__ void sigmoid_gate_kernel(void* __restrict__ x, int dtx, const void* __restrict__ g, int64_t ldg, int dtg, int64_t n, int W) {
+__global__ void sigmoid_gate_kernel(void* __restrict__ x, int dtx, const void* __restrict__ g, int64_t ldg, int dtg, int64_t n, int W, int vec4) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   rb::pdl_trigger();
   rb::pdl_wait();
+  if (vec4) {                                  // 4 elements per thread (rows and base addresses allow 8- / 16-byte accesses)
+    const int64_t i4 = i * 4;
+    if (i4 >= n) return;
+    const int64_t t = i4 / W;
+    const int c = (int)(i4 % W);
+    const float4 gv = rb::ld4_any(g, dtg, t * ldg + c), xv = rb::ld4_any(x, dtx, i4);
+    rb::st4_any(x, dtx, i4, make_float4(xv.x / (1.f + expf(-gv.x)), xv.y / (1.f + expf(-gv.y)), xv.z / (1.f + expf(-gv.z)), xv.w / (1.f + expf(-gv.w))));
+    return;
+  }
   if (i >= n) return;
   const int64_t t = i / W;
   const int c = (int)(i % W);
@@ -172,5 +181,7 @@ extern "C" int rb_latent_query_rope(const void* q, int64_t ldq, int dt, const in
 extern "C" int rb_sigmoid_gate(void* x, int dtx, const void* g, int64_t ldg, int dtg, int64_t T, int W, cudaStream_t s) {
   const int64_t n = T * W;
   if (n == 0) return 0;
-  return rb::launch_pdl(sigmoid_gate_kernel, dim3((unsigned)RB_CEIL_DIV(n, (int64_t)256)), dim3(256), 0, s, x, dtx, g, ldg, dtg, n, W) == cudaSuccess ? 0 : 2;
+  const int vec4 = (W & 3) == 0 && (ldg & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  const int64_t work = vec4 ? n / 4 : n;
+  return rb::launch_pdl(sigmoid_gate_kernel, dim3((unsigned)RB_CEIL_DIV(work, (int64_t)256)), dim3(256), 0, s, x, dtx, g, ldg, dtg, n, W, vec4) == cudaSuccess ? 0 : 2;
 }

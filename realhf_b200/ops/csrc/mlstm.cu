@@ -10,10 +10,14 @@
 // n is carried as one more column of S (a value that is always 1), so the state of a head is [d, dv + 1] and the kernel's raw
 // output row is [S^T q | n . q].
 //
-//   mlstm_scan   one CTA per (sequence, head, chunk of columns).  A group of LPC lanes owns one column of the extended state with
-//                32 rows per lane in registers; q / k / v / gates of 8 tokens are staged in shared memory (q, k as fp32, read back as
-//                16-byte broadcasts); the lanes' partial dot products meet by shuffles.  The same kernel serves packed prompts
-//                (state from zero or from the slot, left in the slot) and decode steps (sequences of one token).
+//   mlstm_scan   one CTA per (sequence, head, chunk of columns).  A column of the extended state depends only on its own value
+//                column, so columns are independent: a group of LPC lanes owns one column with EPL (32 or 64) rows per lane in
+//                registers, and a CTA of four warps 128 / LPC value columns; the first warp of a head's first CTA also carries
+//                the normaliser (DP / 32 rows per lane).  q, k, v and the gates of the next chunk of tokens are fetched into registers (16-byte loads
+//                where the rows allow it) while the current chunk is processed out of shared memory (two staging buffers, one
+//                barrier per chunk; q, k staged as fp32 and read back as 16-byte broadcasts); the lanes' partial dot products meet
+//                by shuffles.  The same kernel serves packed prompts (state from zero or from the slot, left in the slot) and
+//                decode steps (sequences of one token).
 //   mlstm_out    warp per (token, head): the denominator above, the head's RMS norm (no weight), then the full-width weight and
 //                the sigmoid output gate.
 #include "anytype.cuh"
@@ -23,7 +27,7 @@ namespace {
 using rb::ld_any;
 using rb::st_any;
 
-constexpr int kThreads = 128, kTT = 8, kRPL = 32;
+constexpr int kThreads = 128;
 
 struct ScanParams {
   const void* proj; int64_t ld; int dt;   // [T, ld] = [q (H d) | k (H d) | v (H dv) | ... | x_i (H), x_f (H)] at the offsets below
@@ -36,89 +40,193 @@ struct ScanParams {
   const int* slots;                       // [n_seqs] or null (sequence b = slot b)
   int H, d, dv, load_state, off_k, off_v, off_if;
   float cap, qscale;
+  int vec;                                // q / k rows can be read 16 bytes at a time
 };
 
-template <int LPC>
-__global__ void __launch_bounds__(kThreads) mlstm_scan_kernel(ScanParams p) {
+template <typename T> struct Unpack;
+template <> struct Unpack<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void to(const uint4& r, float* f) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+  }
+};
+template <> struct Unpack<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void to(const uint4& r, float* f) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+template <> struct Unpack<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void to(const uint4& r, float* f) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[i])); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+  }
+};
+
+// tokens per staged chunk: the prefetch of a chunk's q and k stays within a few 16-byte registers per thread
+constexpr int chunk_tokens(int dpad) { return dpad <= 256 ? 8 : (dpad <= 512 ? 4 : 2); }
+
+template <typename T, int LPC, int EPL>
+__global__ void __launch_bounds__(kThreads, EPL == 32 ? 3 : 2) mlstm_scan_kernel(ScanParams p) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int COLS = kThreads / LPC, DP = LPC * kRPL;
-  float* qs = smem;                 // [kTT][DP]
-  float* ks = qs + kTT * DP;        // [kTT][DP]
-  float* vs = ks + kTT * DP;        // [kTT][COLS]
-  float* gi = vs + kTT * COLS;      // [kTT]
-  float* gf = gi + kTT;             // [kTT]
-  const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int cl = tid / LPC, l = tid % LPC, col = blockIdx.z * COLS + cl;
+  constexpr int NCOL = kThreads / LPC, DP = LPC * EPL, kTok = chunk_tokens(DP);
+  constexpr int kBuf = 2 * kTok * DP + kTok * NCOL + 2 * kTok;       // floats of one staging buffer: q, k, v, (i, f)
+  constexpr int N = Unpack<T>::N, VPR = DP / N, VQ = kTok * VPR;      // elements per 16-byte load, loads per staged row / chunk
+  constexpr int NQV = (VQ + kThreads - 1) / kThreads, NV = (kTok * NCOL + kThreads - 1) / kThreads;
+  const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, c0 = blockIdx.z * NCOL;
+  constexpr int NR = DP / 32;                                          // normaliser rows per lane: j * 32 + lane
+  const bool norm_warp = tid < 32 && blockIdx.z == 0;                  // this warp also carries the normaliser column (v = 1)
+  const int l = tid % LPC, cl = tid / LPC, lane = tid & 31;
   const int d = p.d, dv = p.dv, dvx = dv + 1, dt = p.dt;
-  const bool active = col <= dv;
+  const int col = c0 + cl;
+  const bool active = col < dv;
   rb::pdl_trigger();
   rb::pdl_wait();
-  const int s0 = p.cu ? p.cu[seq] : seq, L = p.cu ? p.cu[seq + 1] - s0 : 1;
-  if (L <= 0) return;
+  const int t0 = p.cu ? p.cu[seq] : seq, t1 = p.cu ? p.cu[seq + 1] : seq + 1;
+  if (t1 <= t0) return;
   const int64_t slot = p.slots ? p.slots[seq] : seq;
-  const int r0 = l * kRPL;
-  float s[kRPL];
+  auto row_of = [&](int e) { return ((e >> 2) * LPC + l) * 4 + (e & 3); };
+  float S[EPL];
   float m = 0.f;
   float* Sg = p.S ? p.S + ((slot * p.H + h) * (int64_t)d) * dvx : nullptr;
-  if (p.load_state && Sg != nullptr) {
+  const bool load = p.load_state && Sg != nullptr;
 #pragma unroll
-    for (int r = 0; r < kRPL; ++r) s[r] = (active && r0 + r < d) ? Sg[(int64_t)(r0 + r) * dvx + col] : 0.f;
-    m = p.M[slot * p.H + h];
-  } else {
-#pragma unroll
-    for (int r = 0; r < kRPL; ++r) s[r] = 0.f;
+  for (int e = 0; e < EPL; ++e) {
+    const int row = row_of(e);
+    S[e] = (load && active && row < d) ? Sg[(int64_t)row * dvx + col] : 0.f;
   }
-  const unsigned gmask = (LPC == 32) ? 0xffffffffu : (((1u << LPC) - 1u) << ((tid & 31) / LPC * LPC));
-  for (int t0 = 0; t0 < L; t0 += kTT) {
-    const int nt = min(kTT, L - t0);
+  float nrm[NR];
+#pragma unroll
+  for (int j = 0; j < NR; ++j) nrm[j] = (load && norm_warp && j * 32 + lane < d) ? Sg[(int64_t)(j * 32 + lane) * dvx + dv] : 0.f;
+  if (load) m = p.M[slot * p.H + h];
+
+  uint4 rq[NQV], rk[NQV];
+  float rv[NV], rg = 0.f;
+  auto fetch = [&](int tb) {
+    const int nt = min(kTok, t1 - tb);
+    if (p.vec) {
+      const T* src = static_cast<const T*>(p.proj);
+#pragma unroll
+      for (int i = 0; i < NQV; ++i) {
+        const int vi = tid + i * kThreads, tt = vi / VPR, e = (vi % VPR) * N;
+        rq[i] = rk[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (vi < VQ && tt < nt && e < d) {
+          const T* row = src + (int64_t)(tb + tt) * p.ld + h * d + e;
+          rq[i] = *reinterpret_cast<const uint4*>(row);
+          rk[i] = *reinterpret_cast<const uint4*>(row + p.off_k);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = tid + i * kThreads, tt = idx / NCOL, c = c0 + idx % NCOL;
+      rv[i] = (idx < kTok * NCOL && tt < nt && c < dv) ? ld_any(p.proj, dt, (int64_t)(tb + tt) * p.ld + p.off_v + h * dv + c) : 0.f;
+    }
+    const int gt = kThreads - 1 - tid;                                 // the last warp brings the gates: (token, i or f)
+    if (gt < 2 * nt)
+      rg = ld_any(p.proj, dt, (int64_t)(tb + gt / 2) * p.ld + p.off_if + (gt & 1) * p.H + h) + ld_any(p.gate_bias, dt, (gt & 1) * p.H + h);
+  };
+  auto stage = [&](float* buf, int tb) {
+    float* qs = buf;
+    float* ks = buf + kTok * DP;
+    if (p.vec) {
+#pragma unroll
+      for (int i = 0; i < NQV; ++i) {
+        const int vi = tid + i * kThreads;
+        if (vi < VQ) {
+          float fq[N], fk[N];
+          Unpack<T>::to(rq[i], fq);
+          Unpack<T>::to(rk[i], fk);
+#pragma unroll
+          for (int j = 0; j < N; j += 4) {
+            *reinterpret_cast<float4*>(qs + vi * N + j) = make_float4(fq[j] * p.qscale, fq[j + 1] * p.qscale, fq[j + 2] * p.qscale, fq[j + 3] * p.qscale);
+            *reinterpret_cast<float4*>(ks + vi * N + j) = make_float4(fk[j], fk[j + 1], fk[j + 2], fk[j + 3]);
+          }
+        }
+      }
+    } else {                                                           // rows that allow no 16-byte loads: fetched here
+      const int nt = min(kTok, t1 - tb);
+      for (int idx = tid; idx < kTok * DP; idx += kThreads) {
+        const int tt = idx / DP, e = idx % DP;
+        const bool ok = tt < nt && e < d;
+        const int64_t row = (int64_t)(tb + tt) * p.ld;
+        qs[idx] = ok ? ld_any(p.proj, dt, row + h * d + e) * p.qscale : 0.f;
+        ks[idx] = ok ? ld_any(p.proj, dt, row + p.off_k + h * d + e) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kThreads < kTok * NCOL) buf[2 * kTok * DP + tid + i * kThreads] = rv[i];
+    const int gt = kThreads - 1 - tid;
+    if (gt < 2 * kTok) {
+      const float z = p.cap * tanhf(rg / p.cap);
+      buf[2 * kTok * DP + kTok * NCOL + gt] = (gt & 1) ? fminf(z, 0.f) - log1pf(expf(-fabsf(z))) : z;
+    }
+  };
+
+  fetch(t0);
+  int which = 0;
+  for (int tb = t0; tb < t1; tb += kTok, which ^= 1) {
+    const int nt = min(kTok, t1 - tb);
+    float* buf = smem + which * kBuf;
+    stage(buf, tb);
     __syncthreads();
-    for (int idx = tid; idx < nt * DP; idx += kThreads) {
-      const int tt = idx / DP, e = idx % DP;
-      const int64_t row = (int64_t)(s0 + t0 + tt) * p.ld;
-      qs[idx] = e < d ? ld_any(p.proj, dt, row + h * d + e) * p.qscale : 0.f;
-      ks[idx] = e < d ? ld_any(p.proj, dt, row + p.off_k + h * d + e) : 0.f;
-    }
-    for (int idx = tid; idx < nt * COLS; idx += kThreads) {
-      const int tt = idx / COLS, c = blockIdx.z * COLS + idx % COLS;
-      vs[idx] = c < dv ? ld_any(p.proj, dt, (int64_t)(s0 + t0 + tt) * p.ld + p.off_v + h * dv + c) : (c == dv ? 1.f : 0.f);
-    }
-    if (tid < nt) {
-      const int64_t row = (int64_t)(s0 + t0 + tid) * p.ld + p.off_if;
-      const float xi = ld_any(p.proj, dt, row + h) + ld_any(p.gate_bias, dt, h);
-      const float xf = ld_any(p.proj, dt, row + p.H + h) + ld_any(p.gate_bias, dt, p.H + h);
-      gi[tid] = p.cap * tanhf(xi / p.cap);
-      const float z = p.cap * tanhf(xf / p.cap);
-      gf[tid] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-    }
-    __syncthreads();
+    if (tb + kTok < t1) fetch(tb + kTok);
+    const float* qs = buf;
+    const float* ks = buf + kTok * DP;
+    const float* vs = ks + kTok * DP;
+    const float* gs = vs + kTok * NCOL;
+#pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
-      const float ig = gi[tt], fg = gf[tt];
+      const float ig = gs[tt * 2], fg = gs[tt * 2 + 1];
       const float mn = fmaxf(fg + m, ig);
       const float dec = expf(fg + m - mn), inp = expf(ig - mn);
       m = mn;
-      const float v = vs[tt * COLS + cl] * inp;
-      const float* kr = ks + tt * DP + r0;
-      const float* qr = qs + tt * DP + r0;
-      float acc = 0.f;
+      const float v = vs[tt * NCOL + cl] * inp;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DP) + l;
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DP) + l;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < kRPL; r += 4) {
-        const float4 kk = *reinterpret_cast<const float4*>(kr + r), qq = *reinterpret_cast<const float4*>(qr + r);
-        s[r] = fmaf(dec, s[r], kk.x * v);         acc = fmaf(s[r], qq.x, acc);
-        s[r + 1] = fmaf(dec, s[r + 1], kk.y * v); acc = fmaf(s[r + 1], qq.y, acc);
-        s[r + 2] = fmaf(dec, s[r + 2], kk.z * v); acc = fmaf(s[r + 2], qq.z, acc);
-        s[r + 3] = fmaf(dec, s[r + 3], kk.w * v); acc = fmaf(s[r + 3], qq.w, acc);
+      for (int e4 = 0; e4 < EPL / 4; ++e4) {
+        const float4 kk = k4[e4 * LPC], qq = q4[e4 * LPC];
+        S[e4 * 4] = fmaf(dec, S[e4 * 4], kk.x * v);         a0 = fmaf(S[e4 * 4], qq.x, a0);
+        S[e4 * 4 + 1] = fmaf(dec, S[e4 * 4 + 1], kk.y * v); a1 = fmaf(S[e4 * 4 + 1], qq.y, a1);
+        S[e4 * 4 + 2] = fmaf(dec, S[e4 * 4 + 2], kk.z * v); a2 = fmaf(S[e4 * 4 + 2], qq.z, a2);
+        S[e4 * 4 + 3] = fmaf(dec, S[e4 * 4 + 3], kk.w * v); a3 = fmaf(S[e4 * 4 + 3], qq.w, a3);
       }
+      float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
-      for (int o = LPC / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(gmask, acc, o, LPC);
-      const int64_t t = s0 + t0 + tt;
+      for (int off = 1; off < LPC; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      const int64_t t = tb + tt;
       if (l == 0 && active) p.o[(t * p.H + h) * dvx + col] = acc;
+      if (norm_warp) {
+        float nq = 0.f;
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+          nrm[j] = fmaf(dec, nrm[j], ks[tt * DP + j * 32 + lane] * inp);
+          nq = fmaf(nrm[j], qs[tt * DP + j * 32 + lane], nq);
+        }
+        nq = rb::warp_sum(nq);
+        if (lane == 0) p.o[(t * p.H + h) * dvx + dv] = nq;
+      }
       if (tid == 0 && blockIdx.z == 0) p.m_out[t * p.H + h] = m;
     }
   }
   if (Sg != nullptr) {
 #pragma unroll
-    for (int r = 0; r < kRPL; ++r)
-      if (active && r0 + r < d) Sg[(int64_t)(r0 + r) * dvx + col] = s[r];
+    for (int e = 0; e < EPL; ++e) {
+      const int row = row_of(e);
+      if (active && row < d) Sg[(int64_t)row * dvx + col] = S[e];
+    }
+    if (norm_warp) {
+#pragma unroll
+      for (int j = 0; j < NR; ++j)
+        if (j * 32 + lane < d) Sg[(int64_t)(j * 32 + lane) * dvx + dv] = nrm[j];
+    }
     if (tid == 0 && blockIdx.z == 0) p.M[slot * p.H + h] = m;
   }
 }
@@ -146,14 +254,21 @@ __global__ void __launch_bounds__(128) mlstm_out_kernel(const float* __restrict_
   }
 }
 
-template <int LPC>
-int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
-  constexpr int COLS = kThreads / LPC, DP = LPC * kRPL;
-  const size_t smem = sizeof(float) * ((size_t)2 * kTT * DP + (size_t)kTT * COLS + 2 * kTT);
-  auto kern = mlstm_scan_kernel<LPC>;
+template <typename T, int LPC, int EPL>
+int launch_scan_t(const ScanParams& p, int n_seqs, cudaStream_t s) {
+  constexpr int NCOL = kThreads / LPC, DP = LPC * EPL, kTok = chunk_tokens(DP);
+  const size_t smem = sizeof(float) * 2 * ((size_t)2 * kTok * DP + (size_t)kTok * NCOL + 2 * kTok);
+  auto kern = mlstm_scan_kernel<T, LPC, EPL>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
-  dim3 grid((unsigned)n_seqs, (unsigned)p.H, (unsigned)RB_CEIL_DIV(p.dv + 1, COLS));
+  dim3 grid((unsigned)n_seqs, (unsigned)p.H, (unsigned)RB_CEIL_DIV(p.dv, NCOL));
   return rb::launch_pdl(kern, grid, dim3(kThreads), smem, s, p) == cudaSuccess ? 0 : 2;
+}
+
+template <int LPC, int EPL>
+int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
+  if (p.dt == 0) return launch_scan_t<float, LPC, EPL>(p, n_seqs, s);
+  if (p.dt == 1) return launch_scan_t<__nv_bfloat16, LPC, EPL>(p, n_seqs, s);
+  return launch_scan_t<__half, LPC, EPL>(p, n_seqs, s);
 }
 
 }  // namespace
@@ -164,15 +279,16 @@ extern "C" int rb_mlstm_scan(const void* proj, int64_t ld, int dt, const void* g
                              const int* slots, int n_seqs, int H, int d, int dv, int off_k, int off_v, int off_if, float cap, float qscale,
                              int load_state, cudaStream_t s) {
   if (n_seqs == 0) return 0;
-  if (d < 1 || d > 32 * kRPL) return -1;
-  ScanParams p{proj, ld, dt, gate_bias, o, m_out, cu, S, M, slots, H, d, dv, load_state, off_k, off_v, off_if, cap, qscale};
-  const int lanes = RB_CEIL_DIV(d, kRPL);
-  if (lanes <= 1) return launch_scan<1>(p, n_seqs, s);
-  if (lanes <= 2) return launch_scan<2>(p, n_seqs, s);
-  if (lanes <= 4) return launch_scan<4>(p, n_seqs, s);
-  if (lanes <= 8) return launch_scan<8>(p, n_seqs, s);
-  if (lanes <= 16) return launch_scan<16>(p, n_seqs, s);
-  return launch_scan<32>(p, n_seqs, s);
+  if (d < 1 || d > 1024 || dv < 1) return -1;
+  const int n16 = dt == 0 ? 4 : 8;
+  const int vec = d % n16 == 0 && ld % n16 == 0 && off_k % n16 == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
+  ScanParams p{proj, ld, dt, gate_bias, o, m_out, cu, S, M, slots, H, d, dv, load_state, off_k, off_v, off_if, cap, qscale, vec};
+  if (d <= 32) return launch_scan<1, 32>(p, n_seqs, s);
+  if (d <= 64) return launch_scan<2, 32>(p, n_seqs, s);
+  if (d <= 128) return launch_scan<2, 64>(p, n_seqs, s);
+  if (d <= 256) return launch_scan<4, 64>(p, n_seqs, s);
+  if (d <= 512) return launch_scan<8, 64>(p, n_seqs, s);
+  return launch_scan<16, 64>(p, n_seqs, s);
 }
 
 extern "C" int rb_mlstm_out(const float* o, const float* m, const void* w, int dtw, const void* gate, int64_t ldg, int dtg, void* out, int dto,

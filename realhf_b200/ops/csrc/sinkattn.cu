@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(128) value_norm_store_kernel(const void* __res
     const int64_t crow = slot >= 0 ? ((int64_t)slot * Gv + g) * rows + row : 0;
     for (int c = lane; c < dv; c += 32) {
       const float v = ld_any(qkvg, dt, base + ov + g * dv + c) * r;
-      st_any(vout, dt, t * (int64_t)(Gv * dv) + g * dv + c, v);
+      if (vout != nullptr) st_any(vout, dt, t * (int64_t)(Gv * dv) + g * dv + c, v);
       if (slot >= 0) st_any(vc, dt, crow * dv + c, v);
     }
   }
@@ -226,6 +226,16 @@ __global__ void __launch_bounds__(128) qk_head_norm_kernel(void* __restrict__ x,
   const void* w = h < nq ? wq : wk;
   const int64_t base = t * ld + (int64_t)h * d;
   float ss = 0.f;
+  if ((d & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {      // 4 elements per access
+    for (int c = lane * 4; c < d; c += 128) { const float4 v = rb::ld4_any(x, dt, base + c); ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    ss = rb::warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)d + eps);
+    for (int c = lane * 4; c < d; c += 128) {
+      const float4 v = rb::ld4_any(x, dt, base + c);
+      rb::st4_any(x, dt, base + c, make_float4(v.x * r * ld_any(w, dt, c), v.y * r * ld_any(w, dt, c + 1), v.z * r * ld_any(w, dt, c + 2), v.w * r * ld_any(w, dt, c + 3)));
+    }
+    return;
+  }
   for (int c = lane; c < d; c += 32) { const float v = ld_any(x, dt, base + c); ss += v * v; }
   ss = rb::warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)d + eps);
@@ -245,6 +255,20 @@ __global__ void __launch_bounds__(128) diff_combine_kernel(const void* __restric
   const int64_t b1 = (t * 2 * H + (int64_t)(g * 2) * per + hh) * dv, b2 = b1 + (int64_t)per * dv;
   const float l = lam[0];
   float ss = 0.f;
+  if ((dv & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {   // 4 elements per access
+    for (int c = lane * 4; c < dv; c += 128) {
+      const float4 x = rb::ld4_any(a, dta, b1 + c), y = rb::ld4_any(a, dta, b2 + c);
+      const float o0 = x.x - l * y.x, o1 = x.y - l * y.y, o2 = x.z - l * y.z, o3 = x.w - l * y.w;
+      ss += o0 * o0 + o1 * o1 + o2 * o2 + o3 * o3;
+    }
+    ss = rb::warp_sum(ss);
+    const float r = (1.f - diff) / sqrtf(ss / (float)dv + eps);
+    for (int c = lane * 4; c < dv; c += 128) {
+      const float4 x = rb::ld4_any(a, dta, b1 + c), y = rb::ld4_any(a, dta, b2 + c);
+      rb::st4_any(out, dto, id * dv + c, make_float4((x.x - l * y.x) * r, (x.y - l * y.y) * r, (x.z - l * y.z) * r, (x.w - l * y.w) * r));
+    }
+    return;
+  }
   for (int c = lane; c < dv; c += 32) { const float o = ld_any(a, dta, b1 + c) - l * ld_any(a, dta, b2 + c); ss += o * o; }
   ss = rb::warp_sum(ss);
   const float r = (1.f - diff) / sqrtf(ss / (float)dv + eps);
