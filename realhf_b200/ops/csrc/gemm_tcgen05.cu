@@ -617,7 +617,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int nu
   }
   const int tiles = RB_CEIL_DIV(p.M, BM) * RB_CEIL_DIV(p.N, BN);
   if constexpr (kMC == 1) {
-    const int grid = tiles < num_sms ? tiles : num_sms;
+    // grouped: every group with rows has its own m-tiles, so the dense count is no bound; the caller passes min(upper bound, #SMs)
+    const int grid = kMode == 3 ? num_sms : (tiles < num_sms ? tiles : num_sms);
     kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ta, tb, p, fp, peers);
   } else {
     const int padded = RB_CEIL_DIV(tiles, kMC) * kMC;
