@@ -58,6 +58,8 @@ def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: O
         probs = torch.sigmoid(logits).gather(-1, idx) if mcfg.top_k == 1 else torch.softmax(logits, -1).gather(-1, idx)
         return probs, idx
     if mcfg.routing_type == "softmax_all":
+        if bias is None and _native_route(h, w_router, mcfg):
+            return softmax_all_route(h, w_router, correction, mcfg)[:2]
         full = torch.softmax(logits, dim=-1)
         idx = torch.topk(full + correction.float() if correction is not None else full, mcfg.top_k, dim=-1).indices
         probs = full.gather(-1, idx)
@@ -74,6 +76,23 @@ def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: O
         frac_probs = full.mean(0)
         MOE_STATS["aux_loss"].append((frac_tokens * frac_probs).sum() * E * mcfg.aux_loss_coeff / mcfg.top_k)
     return probs, idx
+
+
+def _native_route(h: torch.Tensor, w_router: torch.Tensor, mcfg) -> bool:
+    """The fused routing / combination kernels: inference on CUDA, up to 64 router outputs, up to 8 choices."""
+    from realhf_b200.ops import native_built
+    return (h.is_cuda and not torch.is_grad_enabled() and native_built() and h.dim() == 2 and h.stride(1) == 1 and w_router.shape[0] <= 64
+            and mcfg.top_k <= min(8, w_router.shape[0]) and h.dtype in (torch.float32, torch.bfloat16, torch.float16))
+
+
+def softmax_all_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], mcfg,
+                      w_gate: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """One kernel for routing_type "softmax_all" (inference): fp32 logits W h, softmax over all outputs, the top_k largest of
+    score + correction, their scores as weights; with `w_gate` [1, H] also sigmoid(w_gate . h) per token ([T] fp32)."""
+    from realhf_b200.ops import lib
+    probs, idx, gate = lib().softmax_router(h, w_router.contiguous(), correction.contiguous() if correction is not None else None,
+                                            w_gate.contiguous().view(-1) if w_gate is not None else None, mcfg.top_k, bool(mcfg.renormalize))
+    return probs, idx, (gate if w_gate is not None else None)
 
 
 def _apply_capacity(probs, idx, n_experts: int, mcfg):
@@ -151,8 +170,15 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
     else:
         h = TP.copy_to_tp(h, ctx)
     T, H = h.shape
-    probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"),
-                       model.p.get(f"{i}.mlp.router.correction"))
+    gate_sh = None
+    fused = (mcfg.routing_type == "softmax_all" and model.p.get(f"{i}.mlp.router.bias") is None and not ep and ctx.tp_size == 1
+             and mcfg.capacity_factor is None and _native_route(h, model.p[f"{i}.mlp.router.weight"], mcfg))
+    if fused:       # routing, the shared expert's gate and (below) the weighted sum of the experts' outputs: one kernel each
+        probs, idx, gate_sh = softmax_all_route(h, model.p[f"{i}.mlp.router.weight"], model.p.get(f"{i}.mlp.router.correction"), mcfg,
+                                                model.p[f"{i}.mlp.shared.sg.weight"] if mcfg.shared_ff else None)
+    else:
+        probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"),
+                           model.p.get(f"{i}.mlp.router.correction"))
     n_id = mcfg.identity_experts            # router outputs E .. E + n_id - 1: the expert's output is its input
     if n_id or mcfg.shared_ff:
         assert not ep and ctx.tp_size == 1 and mcfg.capacity_factor is None, "identity / shared experts: single-rank stacks"
@@ -225,11 +251,18 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
     if grouped:
         # the device-side offsets end at expert E: rows of identity experts (sorted last) are not touched by the GEMMs and pass through
         y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E + n_id)[:E], w_gu, w_dn, c.activation_function)
-        if n_id:
+        if n_id and not fused:
             y_sorted = torch.where((flat_e[order] >= E).unsqueeze(-1), x_sorted, y_sorted)
     else:
         counts = torch.bincount(flat_e, minlength=E + n_id).tolist()
         y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, c.activation_function)
+    if fused:
+        from realhf_b200.ops import lib
+        back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
+        out = torch.empty(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
+        lib().moe_combine(y_sorted.contiguous(), h, back, probs.float().contiguous(), idx, _shared_mlp(model, i, h) if mcfg.shared_ff else None, gate_sh,
+                          out, E)
+        return out
     if c.fp32_residual:
         # fp32 combine in a fixed order (an atomic index_add_ would make the sum depend on the run): rows back to (token, choice)
         # order, then the sum over the k choices
@@ -246,7 +279,10 @@ def _add_shared(model, i: int, h: torch.Tensor, mcfg, out: torch.Tensor) -> torc
     """out += shared expert(h) * sigmoid(w_sg . h): an expert every token uses, scaled by one learned gate value per token (fp32)."""
     if not mcfg.shared_ff:
         return out
+    g = torch.sigmoid(F.linear(h.float(), model.p[f"{i}.mlp.shared.sg.weight"].float()))
+    return out + (_shared_mlp(model, i, h).float() * g).to(out.dtype)
+
+
+def _shared_mlp(model, i: int, h: torch.Tensor) -> torch.Tensor:
     p = model.p
-    y = OF.linear(OF.gated_linear(h, p[f"{i}.mlp.shared.gate_up.weight"], model.config.activation_function), p[f"{i}.mlp.shared.down.weight"])
-    g = torch.sigmoid(F.linear(h.float(), p[f"{i}.mlp.shared.sg.weight"].float()))
-    return out + (y.float() * g).to(out.dtype)
+    return OF.linear(OF.gated_linear(h, p[f"{i}.mlp.shared.gate_up.weight"], model.config.activation_function), p[f"{i}.mlp.shared.down.weight"])

@@ -41,6 +41,10 @@ int rb_latent_rope_assemble(const void*, int64_t, const void*, int64_t, const vo
                             int, int, int, cudaStream_t);
 int rb_latent_query_rope(const void*, int64_t, int, const int*, const int*, const float*, float, float, float*, int, int, int, int, int, cudaStream_t);
 int rb_sigmoid_gate(void*, int, const void*, int64_t, int, int64_t, int, cudaStream_t);
+int rb_softmax_router(const void*, int64_t, int, const void*, int, const void*, int, const void*, int, float*, int64_t*, float*, int64_t, int, int, int,
+                      int, cudaStream_t);
+int rb_moe_combine(const void*, int, const void*, int64_t, int, const int64_t*, const float*, const int64_t*, const void*, int, const float*, void*, int,
+                   int64_t, int, int, int, cudaStream_t);
 int rb_qk_head_norm(void*, int64_t, int, const void*, const void*, int64_t, int, int, int, float, cudaStream_t);
 int rb_diff_combine(const void*, int, const float*, void*, int, int64_t, int, int, int, float, float, cudaStream_t);
 }
@@ -179,6 +183,42 @@ void diff_combine(const Tensor& a, const Tensor& lam, Tensor out, int64_t H, int
                               (int)dv, (float)diff, (float)eps, cur_stream()) == 0);
 }
 
+// x [T, K], w [R, K] -> (weights [T, k] fp32, outputs [T, k] int64, gate [T] fp32 or empty): see moe_route.cu
+std::vector<Tensor> softmax_router(const Tensor& x, const Tensor& w, const OptT& corr, const OptT& u, int64_t k, bool renorm) {
+  CHECK_ROWS(x); CHECK_IN(w);
+  const int64_t T = x.size(0), K = x.size(1), R = w.size(0);
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && w.size(1) == K && R <= 64 && k >= 1 && k <= 8 && k <= R, "softmax_router: shapes");
+  if (corr.has_value()) { CHECK_IN((*corr)); TORCH_CHECK(corr->numel() == R); }
+  if (u.has_value()) { CHECK_IN((*u)); TORCH_CHECK(u->numel() == K); }
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor probs = at::empty({T, k}, x.options().dtype(at::kFloat)), idx = at::empty({T, k}, x.options().dtype(at::kLong));
+  Tensor gate = at::empty({u.has_value() ? T : 0}, x.options().dtype(at::kFloat));
+  TORCH_CHECK(rb_softmax_router(x.data_ptr(), x.stride(0), dt_code(x), w.data_ptr(), dt_code(w), corr.has_value() ? corr->data_ptr() : nullptr,
+                                corr.has_value() ? dt_code(*corr) : 0, u.has_value() ? u->data_ptr() : nullptr, u.has_value() ? dt_code(*u) : 0,
+                                probs.data_ptr<float>(), idx.data_ptr<int64_t>(), u.has_value() ? gate.data_ptr<float>() : nullptr, T, (int)K, (int)R,
+                                (int)k, renorm ? 1 : 0, cur_stream()) == 0);
+  return {probs, idx, gate};
+}
+
+// out[t] = sum_j probs[t, j] * (idx[t, j] < E ? y[row[t, j]] : x[t]) + gate[t] * y_shared[t]
+void moe_combine(const Tensor& y, const Tensor& x, const Tensor& row, const Tensor& probs, const Tensor& idx, const OptT& ysh, const OptT& gate,
+                 Tensor out, int64_t E) {
+  CHECK_IN(y); CHECK_ROWS(x); CHECK_IN(row); CHECK_IN(probs); CHECK_IN(idx); CHECK_IN(out);
+  const int64_t T = x.size(0), H = x.size(1), k = probs.size(1);
+  TORCH_CHECK(y.dim() == 2 && y.size(1) == H && out.size(0) == T && out.size(1) == H && probs.size(0) == T && idx.numel() == T * k && row.numel() == T * k);
+  TORCH_CHECK(row.scalar_type() == at::kLong && idx.scalar_type() == at::kLong && probs.scalar_type() == at::kFloat && k <= 8);
+  TORCH_CHECK(ysh.has_value() == gate.has_value());
+  if (ysh.has_value()) {
+    CHECK_IN((*ysh)); CHECK_IN((*gate));
+    TORCH_CHECK(ysh->size(0) == T && ysh->size(1) == H && gate->numel() == T && gate->scalar_type() == at::kFloat);
+  }
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(rb_moe_combine(y.data_ptr(), dt_code(y), x.data_ptr(), x.stride(0), dt_code(x), row.data_ptr<int64_t>(), probs.data_ptr<float>(),
+                             idx.data_ptr<int64_t>(), ysh.has_value() ? ysh->data_ptr() : nullptr, ysh.has_value() ? dt_code(*ysh) : 0,
+                             gate.has_value() ? gate->data_ptr<float>() : nullptr, out.data_ptr(), dt_code(out), T, (int)H, (int)k, (int)E,
+                             cur_stream()) == 0);
+}
+
 }  // namespace
 
 void register_mix_ops(torch::Library& m) {
@@ -188,6 +228,8 @@ void register_mix_ops(torch::Library& m) {
   m.def("latent_rope_assemble(Tensor q, Tensor kn, Tensor lat, Tensor pos, Tensor inv_freq, float mscale, Tensor(a!) out, int H, int d, int rot, int r) -> ()", &latent_rope_assemble);
   m.def("latent_query_rope(Tensor q, Tensor lens, Tensor? slots, Tensor inv_freq, float mscale, float scale, Tensor(a!) qa, int d, int rot) -> ()", &latent_query_rope);
   m.def("sigmoid_gate_(Tensor(a!) x, Tensor gate) -> ()", &sigmoid_gate_);
+  m.def("softmax_router(Tensor x, Tensor w, Tensor? corr, Tensor? u, int k, bool renorm) -> Tensor[]", &softmax_router);
+  m.def("moe_combine(Tensor y, Tensor x, Tensor row, Tensor probs, Tensor idx, Tensor? y_shared, Tensor? gate, Tensor(a!) out, int E) -> ()", &moe_combine);
   m.def("qk_head_norm_(Tensor(a!) x, Tensor wq, Tensor wk, int nq, int nk, int d, float eps) -> ()", &qk_head_norm_);
   m.def("diff_combine(Tensor a, Tensor lam, Tensor(a!) out, int H, int G, int dv, float diff, float eps) -> ()", &diff_combine);
 }

@@ -517,3 +517,48 @@ def test_trace_replay_command(tmp_path, device):
     for s, wl in want.items():
         got = torch.from_numpy(np.fromfile(os.path.join(out, f"{s}.f32"), dtype="<f4").reshape(-1, V))
         assert float(row_errs(got, wl).max()) < 2e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,K,R,k,with_gate", [(1, 64, 1, 1, False), (5, 100, 9, 2, True), (37, 256, 64, 8, True), (300, 2048, 33, 3, False)])
+def test_router_and_combine_kernels_against_plain_torch(dtype, T, K, R, k, with_gate):
+    """Routing by the softmax over all outputs (correction for the choice only) and the weighted sum of expert rows, identity
+    rows and the gated shared output, each one kernel, against the same arithmetic in fp64."""
+    from realhf_b200.ops import lib
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(T * 131 + R)
+    x = torch.randn(T, K, generator=g).to(dtype).to(dev)
+    w = (torch.randn(R, K, generator=g) * K ** -0.5 * 3).to(dtype).to(dev)
+    corr = (torch.randn(R, generator=g) * 0.3).to(dtype).to(dev)
+    u = torch.randn(1, K, generator=g).mul(K ** -0.5).to(dtype).to(dev) if with_gate else None
+    for c, renorm in ((corr, False), (None, True)):
+        probs, idx, gate = lib().softmax_router(x, w, c, u.view(-1) if with_gate else None, k, renorm)
+        s = torch.softmax(x.double() @ w.double().T, -1)
+        choice = s + (c.double() if c is not None else 0.0)
+        want_idx = torch.topk(choice, k, -1).indices
+        # a close call between two choice scores may go either way: compare the chosen scores, and the sets where they are apart
+        got_choice = choice.gather(1, idx)
+        assert torch.allclose(got_choice, choice.gather(1, want_idx), atol=1e-5, rtol=0)
+        want_p = s.gather(1, idx)
+        if renorm:
+            want_p = want_p / want_p.sum(-1, keepdim=True)
+        assert torch.allclose(probs.double(), want_p, atol=1e-5, rtol=1e-5)
+        if with_gate:
+            assert torch.allclose(gate.double(), torch.sigmoid(x.double() @ u.double().view(-1)), atol=1e-5)
+    # combination: E real experts, outputs >= E are identity experts
+    H, E = K, max(R - 2, 1)
+    order = torch.argsort(idx.reshape(-1), stable=True)
+    back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=dev))
+    y = torch.randn(T * k, H, generator=g).to(dtype).to(dev)
+    ysh = torch.randn(T, H, generator=g).to(dtype).to(dev) if with_gate else None
+    for out_dtype in (torch.float32, dtype):
+        out = torch.empty(T, H, dtype=out_dtype, device=dev)
+        lib().moe_combine(y, x, back, probs, idx, ysh, gate if with_gate else None, out, E)
+        rows = y.double()[back].view(T, k, H)
+        rows = torch.where((idx >= E).unsqueeze(-1), x.double().unsqueeze(1), rows)
+        want = (rows * probs.double().unsqueeze(-1)).sum(1)
+        if with_gate:
+            want = want + ysh.double() * gate.double().unsqueeze(-1)
+        tol_ = 1e-5 if out_dtype == torch.float32 else 2e-2
+        assert torch.allclose(out.double(), want, atol=tol_, rtol=tol_)
