@@ -182,6 +182,16 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
     n_id = mcfg.identity_experts            # router outputs E .. E + n_id - 1: the expert's output is its input
     if n_id or mcfg.shared_ff:
         assert not ep and ctx.tp_size == 1 and mcfg.capacity_factor is None, "identity / shared experts: single-rank stacks"
+    if fused and T * k <= 1024 and mcfg.use_grouped_gemm and _use_grouped_kernel(h, w_gu, w_dn):
+        # a decode-sized batch: every assignment's place in the order sorted by expert and the experts' row offsets come from a
+        # counting kernel instead of a sort; rows of identity experts lie behind the last offset and never enter the GEMMs
+        from realhf_b200.ops import gemm as G, lib
+        back, offsets = lib().moe_dispatch(idx, E, E + n_id)
+        hid = G.grouped_linear(lib().moe_gather(h, back, k), w_gu, offsets)
+        y_sorted = G.grouped_linear(OF.gated_act(hid, c.activation_function), w_dn, offsets)
+        out = torch.empty(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
+        lib().moe_combine(y_sorted, h, back, probs, idx, _shared_mlp(model, i, h) if mcfg.shared_ff else None, gate_sh, out, E)
+        return out
     probs = _apply_capacity(probs, idx, E, mcfg)
     flat_e = idx.reshape(-1)
     order = torch.argsort(flat_e, stable=True)

@@ -45,6 +45,8 @@ int rb_softmax_router(const void*, int64_t, int, const void*, int, const void*, 
                       int, cudaStream_t);
 int rb_moe_combine(const void*, int, const void*, int64_t, int, const int64_t*, const float*, const int64_t*, const void*, int, const float*, void*, int,
                    int64_t, int, int, int, cudaStream_t);
+int rb_moe_dispatch(const int64_t*, int64_t*, int*, int, int, int, cudaStream_t);
+int rb_moe_gather(const void*, int64_t, int, const int64_t*, void*, int64_t, int, int, cudaStream_t);
 int rb_qk_head_norm(void*, int64_t, int, const void*, const void*, int64_t, int, int, int, float, cudaStream_t);
 int rb_diff_combine(const void*, int, const float*, void*, int, int64_t, int, int, int, float, float, cudaStream_t);
 }
@@ -219,6 +221,29 @@ void moe_combine(const Tensor& y, const Tensor& x, const Tensor& row, const Tens
                              cur_stream()) == 0);
 }
 
+// idx [T, k] int64 (router outputs, E real experts of R) -> (row [T k] int64: place of each assignment in the order sorted by expert,
+// offsets [E + 1] int32: first row of each real expert); T k <= 1024
+std::vector<Tensor> moe_dispatch(const Tensor& idx, int64_t E, int64_t R) {
+  CHECK_IN(idx);
+  const int64_t N = idx.numel();
+  TORCH_CHECK(idx.scalar_type() == at::kLong && N >= 1 && N <= 1024 && R <= 64 && E <= R, "moe_dispatch: shapes");
+  c10::cuda::CUDAGuard g(idx.device());
+  Tensor row = at::empty({N}, idx.options()), offsets = at::empty({E + 1}, idx.options().dtype(at::kInt));
+  TORCH_CHECK(rb_moe_dispatch(idx.data_ptr<int64_t>(), row.data_ptr<int64_t>(), offsets.data_ptr<int>(), (int)N, (int)E, (int)R, cur_stream()) == 0);
+  return {row, offsets};
+}
+
+// x [T, H], row [T k] -> xs [T k, H] with xs[row[i]] = x[i / k]
+Tensor moe_gather(const Tensor& x, const Tensor& row, int64_t k) {
+  CHECK_ROWS(x); CHECK_IN(row);
+  TORCH_CHECK(row.scalar_type() == at::kLong && row.numel() == x.size(0) * k);
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor xs = at::empty({row.numel(), x.size(1)}, x.options());
+  TORCH_CHECK(rb_moe_gather(x.data_ptr(), x.stride(0), dt_code(x), row.data_ptr<int64_t>(), xs.data_ptr(), row.numel(), (int)x.size(1), (int)k,
+                            cur_stream()) == 0);
+  return xs;
+}
+
 }  // namespace
 
 void register_mix_ops(torch::Library& m) {
@@ -228,6 +253,8 @@ void register_mix_ops(torch::Library& m) {
   m.def("latent_rope_assemble(Tensor q, Tensor kn, Tensor lat, Tensor pos, Tensor inv_freq, float mscale, Tensor(a!) out, int H, int d, int rot, int r) -> ()", &latent_rope_assemble);
   m.def("latent_query_rope(Tensor q, Tensor lens, Tensor? slots, Tensor inv_freq, float mscale, float scale, Tensor(a!) qa, int d, int rot) -> ()", &latent_query_rope);
   m.def("sigmoid_gate_(Tensor(a!) x, Tensor gate) -> ()", &sigmoid_gate_);
+  m.def("moe_dispatch(Tensor idx, int E, int R) -> Tensor[]", &moe_dispatch);
+  m.def("moe_gather(Tensor x, Tensor row, int k) -> Tensor", &moe_gather);
   m.def("softmax_router(Tensor x, Tensor w, Tensor? corr, Tensor? u, int k, bool renorm) -> Tensor[]", &softmax_router);
   m.def("moe_combine(Tensor y, Tensor x, Tensor row, Tensor probs, Tensor idx, Tensor? y_shared, Tensor? gate, Tensor(a!) out, int E) -> ()", &moe_combine);
   m.def("qk_head_norm_(Tensor(a!) x, Tensor wq, Tensor wk, int nq, int nk, int d, float eps) -> ()", &qk_head_norm_);

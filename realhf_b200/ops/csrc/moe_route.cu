@@ -7,6 +7,8 @@
 //   moe_combine      one CTA per token: out[t] = sum_j p[t, j] * (e[t, j] < E ? y[row[t, j]] : x[t]) + g[t] * y_shared[t], summed in the
 //                    order written, in fp32; y holds the expert outputs of the assignments sorted by expert, row[t, j] the place of
 //                    assignment (t, j) in that order; outputs e >= E are identity experts.
+//   moe_dispatch     up to 1024 assignments: their places in the order sorted by expert and the experts' row offsets, one CTA.
+//   moe_gather       the token rows copied into that order.
 #include "anytype.cuh"
 
 namespace {
@@ -143,6 +145,52 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const void* __restrict
   }
 }
 
+// Small batches (N = T k assignments <= 1024): the place of every assignment in the order sorted by expert (stable: equal experts keep
+// the order of (token, choice)) and the row offsets of the first E experts, by one CTA, without a sort.
+__global__ void __launch_bounds__(1024) moe_dispatch_kernel(const int64_t* __restrict__ idx, int64_t* __restrict__ back, int* __restrict__ offsets,
+                                                            int N, int E, int R) {
+  __shared__ int s_e[1024];
+  __shared__ int s_cnt[kMaxOutputs], s_start[kMaxOutputs + 1];
+  const int i = threadIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  if (i < R) s_cnt[i] = 0;
+  if (i < N) s_e[i] = (int)idx[i];
+  __syncthreads();
+  int rank = 0, e = 0;
+  if (i < N) {
+    e = s_e[i];
+    for (int j = 0; j < i; ++j) rank += s_e[j] == e ? 1 : 0;
+    atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (i == 0) {
+    int acc = 0;
+    for (int x = 0; x < R; ++x) { s_start[x] = acc; acc += s_cnt[x]; }
+    s_start[R] = acc;
+  }
+  __syncthreads();
+  if (i < N) back[i] = s_start[e] + rank;
+  if (i <= E) offsets[i] = s_start[i];
+}
+
+// xs[row[i]] = x[i / k]: the token rows laid out in the sorted order
+__global__ void __launch_bounds__(128) moe_gather_kernel(const void* __restrict__ x, int64_t ldx, int dt, const int64_t* __restrict__ row,
+                                                         void* __restrict__ xs, int H, int k) {
+  const int64_t i = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const int64_t src = (i / k) * ldx, dst = row[i] * (int64_t)H;
+  const int es = rb::elt_size(dt);
+  if (((H * es) & 15) == 0 && ((ldx * es) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0) {
+    const uint4* a = reinterpret_cast<const uint4*>(static_cast<const char*>(x) + src * es);
+    uint4* b = reinterpret_cast<uint4*>(static_cast<char*>(xs) + dst * es);
+    for (int c = threadIdx.x; c < H * es / 16; c += blockDim.x) b[c] = a[c];
+    return;
+  }
+  for (int c = threadIdx.x; c < H; c += blockDim.x) rb::st_any(xs, dt, dst + c, ld_any(x, dt, src + c));
+}
+
 }  // namespace
 
 extern "C" int rb_softmax_router(const void* x, int64_t ldx, int dtx, const void* w, int dtw, const void* corr, int dtc, const void* u, int dtu,
@@ -159,4 +207,14 @@ extern "C" int rb_moe_combine(const void* y, int dty, const void* x, int64_t ldx
   if (k < 1 || k > kMaxTop) return -1;
   return rb::launch_pdl(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, s, y, dty, x, ldx, dtx, row, probs, idx, ysh, dts, gate, out, dto, H, k,
                         E) == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int rb_moe_dispatch(const int64_t* idx, int64_t* back, int* offsets, int N, int E, int R, cudaStream_t s) {
+  if (N < 1 || N > 1024 || R > kMaxOutputs || E > R) return -1;
+  return rb::launch_pdl(moe_dispatch_kernel, dim3(1), dim3(1024), 0, s, idx, back, offsets, N, E, R) == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int rb_moe_gather(const void* x, int64_t ldx, int dt, const int64_t* row, void* xs, int64_t N, int H, int k, cudaStream_t s) {
+  if (N == 0) return 0;
+  return rb::launch_pdl(moe_gather_kernel, dim3((unsigned)N), dim3(128), 0, s, x, ldx, dt, row, xs, H, k) == cudaSuccess ? 0 : 2;
 }

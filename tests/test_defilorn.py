@@ -552,6 +552,13 @@ def test_router_and_combine_kernels_against_plain_torch(dtype, T, K, R, k, with_
     back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=dev))
     y = torch.randn(T * k, H, generator=g).to(dtype).to(dev)
     ysh = torch.randn(T, H, generator=g).to(dtype).to(dev) if with_gate else None
+    if T * k <= 1024:       # the counting kernel gives the same places as the stable sort, and the offsets of the real experts
+        row, offsets = lib().moe_dispatch(idx, E, R)
+        assert torch.equal(row, back)
+        counts = torch.bincount(idx.reshape(-1), minlength=R)[:E]
+        assert offsets.tolist() == [0] + counts.cumsum(0).tolist()
+        xs = lib().moe_gather(x, row, k)
+        assert torch.equal(xs[row], x.repeat_interleave(k, 0))
     for out_dtype in (torch.float32, dtype):
         out = torch.empty(T, H, dtype=out_dtype, device=dev)
         lib().moe_combine(y, x, back, probs, idx, ysh, gate if with_gate else None, out, E)
