@@ -296,3 +296,4 @@ register_hf_family(
 from realhf_b200.api.from_hf import rapodra  # noqa: E402,F401  (registers the family)
 from realhf_b200.api.from_hf import tizodra  # noqa: E402,F401  (registers the family)
 from realhf_b200.api.from_hf import defilorn  # noqa: E402,F401  (registers the family)
+from realhf_b200.api.from_hf import buvesun  # noqa: E402,F401  (registers the family)

@@ -65,6 +65,10 @@ class ReaLMoEConfig:
     renormalize: bool = True
     identity_experts: int = 0      # the router has num_experts + identity_experts outputs; the last ones pass their input through
     shared_ff: Optional[int] = None  # a shared expert of this width runs for every token, times sigmoid(w_sg . x) (one number per token)
+    # routing_type "sigmoid": scores = sigmoid(logit) of every router output on its own, the top_k largest are chosen and weigh.
+    scale_input: bool = False      # the routing weight multiplies the expert's INPUT, expert(w x), instead of its output
+    shared_gate: bool = True       # False: the shared expert's output is added as it is (no `mlp.shared.sg.weight`)
+    shared_limit: Optional[float] = None  # clamp limit of the shared expert when the experts are clamped units (None: the experts' own)
 
     @property
     def n_router_outputs(self) -> int:
@@ -153,7 +157,10 @@ class LatentAttentionConfig:
 @dataclasses.dataclass
 class WindowAttentionConfig:
     """Softmax attention over cached keys / values with grouped key / value heads (query head h reads head h // (n_heads /
-    n_kv_heads)) and no rotation.  Every further mechanism is a switch or a constant, so that families can combine them:
+    n_kv_heads)).  Every further mechanism is a switch or a constant, so that families can combine them:
+
+      * `rotary`: queries and keys are rotated by their position over the first `rotary.dims` dimensions of every head (pairs
+        (2i, 2i + 1) when `rotary.interleaved`, else (i, i + dims / 2)); keys are cached rotated.  None: no rotation;
 
       * `window` / `keep_first`: query i sees key j <= i when i - j < window or j < keep_first (window None: all j <= i).  The
         cache of a sequence is then `keep_first` fixed rows plus a ring of `window` rows, whatever the sequence's length;
@@ -182,8 +189,13 @@ class WindowAttentionConfig:
     qk_norm: bool = False
     n_maps: int = 1
     diff: float = 0.0
+    rotary: Optional[RotaryConfig] = None
 
     def __post_init__(self):
+        if isinstance(self.rotary, dict):
+            self.rotary = RotaryConfig(**self.rotary)
+        if self.rotary is not None and (self.rotary.dims % 2 or not 0 < self.rotary.dims <= self.qk_dim or self.n_maps != 1):
+            raise ValueError("rotary.dims: even, at most qk_dim, one score map")
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
         if self.n_maps not in (1, 2):
@@ -240,6 +252,46 @@ class MLSTMConfig:
 
 
 @dataclasses.dataclass
+class DecayConfig:
+    """Linear attention with a fixed decay per head (retention, lightning attention): per head a matrix state S [qk_dim, v_dim]
+    (fp32, from zero), S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; no softmax, no denominator.  Switches:
+
+      * `act`: "silu" puts SiLU on the projected q, k and v; "none" leaves them;
+      * `rotary`: q and k are rotated by the position (fp32) over the first `rotary.dims` dimensions of every head, in the half
+        layout (i, i + dims / 2) or the interleaved one;
+      * `k_scale`: a factor on k (after the rotation), e.g. qk_dim^(-1/2);
+      * `out_norm`: "head": every head's o is divided by its root mean square (no weight); "full": the concatenated heads are
+        RMS-normalised together, times a weight [n_heads * v_dim];
+      * `gate`: the normalised output is multiplied by silu(W_g x) ("silu") or sigmoid(W_g x) ("sigmoid"), x the mixer's input.
+    The projection row is [q (H d) | k (H d) | v (H dv) | gate (H dv)]."""
+    n_heads: int
+    qk_dim: int
+    v_dim: int
+    decay: List[float]
+    act: str = "none"              # none | silu
+    rotary: Optional[RotaryConfig] = None
+    k_scale: float = 1.0
+    out_norm: str = "head"         # head | full
+    gate: str = "silu"             # silu | sigmoid
+
+    def __post_init__(self):
+        if isinstance(self.rotary, dict):
+            self.rotary = RotaryConfig(**self.rotary)
+        self.decay = [float(g) for g in self.decay]
+        if len(self.decay) != self.n_heads:
+            raise ValueError("`decay` needs one value per head")
+        if self.act not in ("none", "silu") or self.out_norm not in ("head", "full") or self.gate not in ("silu", "sigmoid"):
+            raise ValueError("act: none | silu; out_norm: head | full; gate: silu | sigmoid")
+        if self.rotary is not None and (self.rotary.dims % 2 or not 0 < self.rotary.dims <= self.qk_dim):
+            raise ValueError("rotary.dims: even and at most qk_dim")
+
+    @property
+    def width(self) -> int:
+        """Columns of the projection row."""
+        return 2 * self.n_heads * (self.qk_dim + self.v_dim)
+
+
+@dataclasses.dataclass
 class LoopConfig:
     """Blocks start .. stop - 1 (0-based) run `times` times in a row with the same weights, every pass with a cache / state of its
     own.  With `inject`, the embedding output x0 is mixed back in at the start of a pass: mode "linear": every pass,
@@ -257,7 +309,8 @@ class BlockMLPConfig:
     g = min(gate, limit), u = clamp(up, -limit, limit); kind `moe`: `moe.num_experts` SiLU-gated experts of width `ff`, the
     `moe.top_k` largest router logits (with a router bias) are chosen and weighted by the softmax over the chosen logits;
     kind `relu2`: down(relu(up(x))^2), no gate; kind `glu`: down(act(gate(x)) * up(x)) with `act` silu or gelu_tanh.  The experts
-    of kind `moe` are SiLU-gated units of width `ff`; routing variants are fields of `moe`."""
+    of kind `moe` are SiLU-gated units of width `ff`, or, with `limit` > 0, clamped units (the `clamped_glu` form with `limit` and
+    `alpha`); routing variants are fields of `moe`."""
     kind: str                      # clamped_glu | moe | relu2 | glu
     ff: int
     limit: float = 0.0
@@ -269,12 +322,16 @@ class BlockMLPConfig:
 @dataclasses.dataclass
 class BlockConfig:
     """One entry of `ReaLModelConfig.blocks` (a stack whose blocks differ from each other)."""
-    mixer: str                     # latent_attention | window_attention | delta | mlstm
+    mixer: str                     # latent_attention | window_attention | delta | mlstm | decay | parallel
     attn: Optional[LatentAttentionConfig] = None
     mlp: Optional[BlockMLPConfig] = None   # None: the block has no feed-forward sublayer
     wattn: Optional[WindowAttentionConfig] = None
     delta: Optional[DeltaRuleConfig] = None
     mlstm: Optional[MLSTMConfig] = None
+    decay: Optional[DecayConfig] = None
+    # mixer "parallel": `wattn` and `decay` read the same input side by side; the result is branch_scales[0] * window attention +
+    # branch_scales[1] * decayed linear attention (each after its own output projection)
+    branch_scales: Tuple[float, float] = (1.0, 1.0)
 
     def __post_init__(self):
         if isinstance(self.attn, dict):
@@ -285,7 +342,11 @@ class BlockConfig:
             self.delta = DeltaRuleConfig(**self.delta)
         if isinstance(self.mlstm, dict):
             self.mlstm = MLSTMConfig(**self.mlstm)
-        want = {"latent_attention": self.attn, "window_attention": self.wattn, "delta": self.delta, "mlstm": self.mlstm}
+        if isinstance(self.decay, dict):
+            self.decay = DecayConfig(**self.decay)
+        self.branch_scales = (float(self.branch_scales[0]), float(self.branch_scales[1]))
+        want = {"latent_attention": self.attn, "window_attention": self.wattn, "delta": self.delta, "mlstm": self.mlstm, "decay": self.decay,
+                "parallel": self.wattn if self.decay is not None else None}
         if self.mixer not in want:
             raise ValueError(f"unknown mixer `{self.mixer}`")
         if want[self.mixer] is None:
@@ -316,7 +377,7 @@ class ReaLModelConfig:
     use_attention_bias: bool = True
     use_attn_proj_bias: bool = True
     use_mlp_bias: bool = True
-    layer_norm_type: Optional[str] = None  # None (LayerNorm) | "rms" | "gemma"
+    layer_norm_type: Optional[str] = None  # None (LayerNorm) | "rms" | "gemma" | "layer" (heterogeneous stacks: LayerNorm, no bias)
     mlp_type: Optional[str] = None  # None (plain MLP) | "llama" | "moe"
     apply_rotary: bool = False
     rotary_base: float = 10000.0
@@ -343,6 +404,10 @@ class ReaLModelConfig:
     sinusoid_base: float = 10000.0
     logit_scale: Optional[float] = None  # logits <- logits * logit_scale (fp32)
     loop: Optional[LoopConfig] = None    # a range of blocks that runs several times (heterogeneous stacks only)
+    embed_scale: Optional[float] = None  # the embedding output is multiplied by this constant
+    residual_mult: float = 1.0           # x <- x + residual_mult * branch ("layer" stacks)
+    layer_scale: bool = False            # every branch output (after its output norm) times a learned vector (`attn.ls.weight`,
+                                         # `mlp.ls.weight`) before it joins the stream ("layer" stacks)
 
     def layer_runs(self) -> List[Tuple[int, bool]]:
         """(1-based block index, the run starts a pass of the loop) for every block run, in execution order."""
@@ -370,6 +435,11 @@ class ReaLModelConfig:
             self.blocks = [BlockConfig(**b) if isinstance(b, dict) else b for b in self.blocks]
             if len(self.blocks) != self.n_layers:
                 raise ValueError("`blocks` must describe every layer")
+            if self.layer_norm_type == "layer" and (self.norm_groups != 1 or self.conv_taps or not self.sandwich_norm):
+                raise ValueError("\"layer\" stacks: one norm group, no convolution, norms on both sides of every sublayer")
+            if self.layer_norm_type != "layer" and (self.layer_scale or self.residual_mult != 1.0
+                                                    or any(b.mixer in ("decay", "parallel") for b in self.blocks)):
+                raise ValueError("layer_scale, residual_mult and the decay / parallel mixers live in \"layer\" stacks")
             for i, b in enumerate(self.blocks):
                 if b.mixer != "latent_attention":
                     continue
@@ -389,9 +459,15 @@ class ReaLModelConfig:
         h, f, v = self.hidden_dim, self.intermediate_dim, self.vocab_size
         if self.blocks is not None:
             n = 2 * v * h + h
-            norms = (2 if self.sandwich_norm else 1) + self.conv_taps       # per sublayer: norm(s) and convolution taps, times h
+            norms = (2 if self.sandwich_norm else 1) + self.conv_taps + int(self.layer_scale)   # per sublayer: norm(s), taps, scale
             for b in self.blocks:
-                if b.mixer == "window_attention":
+                if b.mixer in ("decay", "parallel"):
+                    a = b.decay
+                    n += h * a.width + a.n_heads * a.v_dim * (h + (1 if a.out_norm == "full" else 0)) + norms * h
+                    if b.mixer == "parallel":
+                        w = b.wattn
+                        n += h * (w.n_heads * w.qk_dim + w.n_kv_heads * (w.qk_dim + w.v_dim)) + w.n_heads * w.v_dim * h
+                elif b.mixer == "window_attention":
                     a = b.wattn
                     qkv = a.n_heads * a.qk_dim + a.n_kv_heads * (a.qk_dim + a.v_dim)
                     qkv += (a.n_maps - 1) * (a.n_heads + a.n_kv_heads) * a.qk_dim
@@ -422,9 +498,9 @@ class ReaLModelConfig:
                     n += e * mats * h * b.mlp.ff + norms * h
                     if b.mlp.kind == "moe":
                         mo = b.mlp.moe
-                        if mo.routing_type == "softmax_all":
+                        if mo.routing_type in ("softmax_all", "sigmoid"):
                             n += mo.n_router_outputs * (h + (1 if mo.score_correction else 0))
-                            n += (3 * h * mo.shared_ff + h) if mo.shared_ff else 0
+                            n += (3 * h * mo.shared_ff + (h if mo.shared_gate else 0)) if mo.shared_ff else 0
                         else:
                             n += e * (h + 1)
             if self.loop is not None and self.loop.inject and self.loop.inject_mode == "linear":

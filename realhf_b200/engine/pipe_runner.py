@@ -258,7 +258,8 @@ class PipelineRunner:
         use_graph = g.use_cuda_graph and dev.type == "cuda"
 
         def stage_step(st):
-            h = m.decode_step(st.input_ids if self.first else None, st.k, st.v, st.cache_lens, hidden=None if self.first else st.hidden_in)
+            h = m.decode_step(st.input_ids if self.first else None, st.k, st.v, st.cache_lens, hidden=None if self.first else st.hidden_in,
+                              m_caches=getattr(st, "m", None))
             out = gen._final_logits(m, h) if self.last else h
             st.cache_lens += 1
             return out

@@ -118,12 +118,23 @@ class DecodeState:
             from realhf_b200.models import hetero_block as HB
             first = model.layers[0] if model.layers[0] >= 1 else 1
             self.k, self.v = [], []
+            self.m: List[Optional[torch.Tensor]] = []   # a third state tensor per run for blocks that hold one (mixer "parallel"), else None
             # tensors a slot's allocation zeroes / a decode step changes beyond an idempotent append: (tensor, slot dim)
             self.zeroed: List[Tuple[torch.Tensor, int]] = []
             run_of_block = {}
             for r, (i, _) in enumerate(model.local_runs()):
                 b = c.blocks[i - 1]
-                if b.mixer == "window_attention":
+                self.m.append(None)
+                if b.mixer in ("decay", "parallel"):
+                    d = b.decay
+                    mat = torch.zeros(B, d.n_heads, d.qk_dim, d.v_dim, dtype=torch.float32, device=dev)
+                    self.zeroed.append((mat, 0))
+                    if b.mixer == "decay":
+                        self.k.append(mat)
+                        self.v.append(torch.zeros(B, 0, dtype=torch.float32, device=dev))
+                        continue
+                    self.m[-1] = mat
+                if b.mixer in ("window_attention", "parallel"):
                     w = b.wattn
                     rows = w.cache_rows(S)
                     self.k.append(torch.zeros(B, w.n_kv_heads * w.n_maps, rows, w.qk_dim, dtype=dt, device=dev))   # every map's keys
@@ -287,8 +298,8 @@ class StepSession:
         B = max(2 * old.B, old.B + n_needed - len(old.free_slots))
         new = DecodeState(self.model, B, self.max_len)
         done = set()
-        for a, b_ in zip(old.k + old.v + [old.cache_lens], new.k + new.v + [new.cache_lens]):
-            if id(a) in done:
+        for a, b_ in zip(old.k + old.v + old.m + [old.cache_lens], new.k + new.v + new.m + [new.cache_lens]):
+            if a is None or id(a) in done:
                 continue
             done.add(id(a))
             b_.narrow(old.slot_dim(a), 0, old.B).copy_(a)
@@ -320,7 +331,7 @@ class StepSession:
         slots = torch.tensor([self.slot_of[r] for r, _ in requests], dtype=torch.int32, device=dev)
         ids = torch.tensor([t for _, t in requests], dtype=torch.long, device=dev)
         st = self.state
-        h = self.model.decode_step(ids, st.k, st.v, st.cache_lens, slots=slots)
+        h = self.model.decode_step(ids, st.k, st.v, st.cache_lens, slots=slots, m_caches=st.m)
         st.cache_lens[slots.long()] += 1
         return h
 
@@ -386,7 +397,7 @@ def generate(model: ReaLModel, input_ids: torch.Tensor, cu_seqlens: torch.Tensor
     need_mask = mb is not None
 
     def one_step():
-        h = model.decode_step(state.input_ids, state.k, state.v, state.cache_lens)
+        h = model.decode_step(state.input_ids, state.k, state.v, state.cache_lens, m_caches=getattr(state, "m", None))
         return _final_logits(model, h)
 
     sig = (in_graph, g.max_new_tokens, g.min_new_tokens, g.top_k, g.top_p, g.temperature, g.greedy, need_mask, eos_id, pad_id,
@@ -595,7 +606,7 @@ class InflightBatchingGenerator:
             active = [s for s in range(self.B) if self.slot_seq[s] >= 0]
             if not active:
                 continue
-            h = m.decode_step(st.input_ids, st.k, st.v, st.cache_lens)
+            h = m.decode_step(st.input_ids, st.k, st.v, st.cache_lens, m_caches=getattr(st, "m", None))
             logits = _final_logits(m, h)
             st.cache_lens += self.unfinished.int()
             # per-slot step index decides whether EOS is still suppressed

@@ -16,7 +16,14 @@ per run (`state.k[r]`, `state.v[r]`), by mixer:
   * differential window attention (`n_maps` = 2): `k[r]` [n_slots, 2G, rows, d] (both maps' keys), `v[r]` [n_slots, G, rows, dv];
   * rotated latent attention: `k[r]` the ring [n_slots, R, kv_rank + rot_dim] of rows [latent | rotated key part], `v[r]` empty;
   * matrix-memory LSTM: `k[r]` the states with the normaliser as last column [n_slots, H, d, dv + 1] fp32, `v[r]` the running
-    maxima [n_slots, H] fp32.
+    maxima [n_slots, H] fp32;
+  * decayed linear attention (`decay`): `k[r]` the matrix states [n_slots, H, d, dv] fp32, `v[r]` empty;
+  * `parallel` (window attention beside decayed linear attention): `k[r]`, `v[r]` the rotated keys / values as for window
+    attention, and a third tensor `state.m[r]` with the matrix states [n_slots, H, d, dv] fp32 (`m[r]` is None for other mixers).
+
+A stack with `layer_norm_type == "layer"` runs  x <- x + mult * ls * LN_post(mixer(LN(x)))  and the same for the feed-forward, LN
+being the bias-free LayerNorm; the add, the branch's output norm and the next sublayer's input norm are one kernel
+(`ops.functional.residual_add_centred_norm_`).
 
 Inference only (no autograd through these kernels) and not tensor-parallel.  A stack with a loop runs on one pipeline stage.
 """
@@ -45,6 +52,7 @@ class PackedMeta:
     cu_seqlens: Optional[torch.Tensor] = None
     max_seqlen: Optional[int] = None
     seq_slot: Optional[torch.Tensor] = None   # [n_seqs] int32 state slot of every sequence (None: keep no state)
+    m: Optional[List[Optional[torch.Tensor]]] = None   # DecodeState.m
 
 
 def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tensor] = None, state=None,
@@ -60,14 +68,15 @@ def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tens
         tok_slot = slots.to(dev).int()[seq].contiguous()
     return PackedMeta(pos, remain, tok_slot, state.k if state is not None else None, state.v if state is not None else None,
                       cu_seqlens=cu_seqlens.int().contiguous(), max_seqlen=max_seqlen,
-                      seq_slot=slots.to(dev).int().contiguous() if slots is not None else None)
+                      seq_slot=slots.to(dev).int().contiguous() if slots is not None else None,
+                      m=getattr(state, "m", None) if state is not None else None)
 
 
 def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
     p = model.p
     if mcfg.kind == "moe":
         from realhf_b200.models import moe
-        return moe.moe_forward(model, i, h, mcfg.moe)
+        return moe.moe_forward(model, i, h, mcfg.moe, clamp=(mcfg.limit, mcfg.alpha) if mcfg.limit > 0 else None)
     if mcfg.kind == "relu2":
         return OF.linear(OF.relu2_linear(h, p[f"{i}.mlp.up.weight"]), p[f"{i}.mlp.down.weight"])
     if mcfg.kind == "glu":
@@ -86,6 +95,8 @@ def _window_attention_packed(model, i: int, li: int, h: torch.Tensor, meta: Pack
                                            c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None, meta.tok_slot,
                                            meta.pos, meta.remain, meta.cu_seqlens, meta.max_seqlen)
         return OF.linear(o, p[f"{i}.attn.o.weight"])
+    if a.rotary is not None:
+        attn_ops.rotate_qk_(qkvg, a, pos=meta.pos)
     v_n = attn_ops.value_norm_store(qkvg, a, c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None,
                                     meta.tok_slot, meta.pos, meta.remain)
     o = attn_ops.sink_window_attention(qkvg, v_n, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), meta.pos,
@@ -101,6 +112,8 @@ def _window_attention_decode(model, i: int, li: int, h: torch.Tensor, k_caches, 
         o = attn_ops.diff_window_decode_attention(qkvg, a, p[f"{i}.attn.q_norm.weight"], p[f"{i}.attn.k_norm.weight"], p[f"{i}.attn.lambda.weight"],
                                                   c.layer_norm_epsilon, k_caches[li], v_caches[li], cache_lens, slots)
         return OF.linear(o, p[f"{i}.attn.o.weight"])
+    if a.rotary is not None:
+        attn_ops.rotate_qk_(qkvg, a, cache_lens=cache_lens, slots=slots)
     o = attn_ops.sink_window_decode_attention(qkvg, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), k_caches[li],
                                               v_caches[li], cache_lens, slots, c.layer_norm_epsilon)
     return OF.linear(o, p[f"{i}.attn.o.weight"])
@@ -196,6 +209,82 @@ def _latent_rope_decode(model, i: int, li: int, h: torch.Tensor, k_caches, cache
     return OF.linear(_latent_rope_gate(a, o, proj), p[f"{i}.attn.o.weight"])
 
 
+def _decay_branch(model, i: int, d, proj: torch.Tensor, o: torch.Tensor) -> torch.Tensor:
+    """Output norm and gate of a decayed-linear-attention branch; `proj` is the branch's projection row [q | k | v | gate]."""
+    g0 = 2 * d.n_heads * d.qk_dim + d.n_heads * d.v_dim
+    return rec_ops.decay_out(o, d, model.p.get(f"{i}.attn.o_norm.weight"), proj[:, g0:g0 + d.n_heads * d.v_dim], model.config.layer_norm_epsilon,
+                             model.dtype)
+
+
+def _decay_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta):
+    p = model.p
+    d = model.config.blocks[i - 1].decay
+    keep = meta.k is not None
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    o = rec_ops.decay_scan(rec_ops.decay_prepare(proj, d, pos=meta.pos), d, meta.cu_seqlens, meta.k[li] if keep else None,
+                           meta.seq_slot if keep else None)
+    return OF.linear(_decay_branch(model, i, d, proj, o), p[f"{i}.attn.o.weight"])
+
+
+def _decay_decode(model, i: int, li: int, h: torch.Tensor, k_caches, cache_lens, slots):
+    p = model.p
+    d = model.config.blocks[i - 1].decay
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    o = rec_ops.decay_step(rec_ops.decay_prepare(proj, d, cache_lens=cache_lens, slots=slots), d, k_caches[li], slots)
+    return OF.linear(_decay_branch(model, i, d, proj, o), p[f"{i}.attn.o.weight"])
+
+
+def _parallel_split(b, proj: torch.Tensor):
+    """The fused projection row of a `parallel` block as two views: [window attention q | k | v] and [decay q | k | v | gate]."""
+    from realhf_b200.models.sharding import wattn_sections
+    nl = sum(wattn_sections(b.wattn))
+    return proj[:, :nl], proj[:, nl:]
+
+
+def _parallel_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta):
+    """Both branches of a `parallel` block on the packed batch -> (left output, right output), each after its own projection."""
+    c, p = model.config, model.p
+    b = c.blocks[i - 1]
+    w, d = b.wattn, b.decay
+    keep = meta.k is not None
+    left, right = _parallel_split(b, OF.linear(h, p[f"{i}.attn.in.weight"]))
+    if w.rotary is not None:
+        attn_ops.rotate_qk_(left, w, pos=meta.pos)
+    v_n = attn_ops.value_norm_store(left, w, c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None, meta.tok_slot,
+                                    meta.pos, meta.remain)
+    o = attn_ops.sink_window_attention(left, v_n, w, None, None, meta.pos, meta.cu_seqlens, meta.max_seqlen)
+    y_l = OF.linear(o, p[f"{i}.attn.o.weight"])
+    s = rec_ops.decay_scan(rec_ops.decay_prepare(right, d, pos=meta.pos), d, meta.cu_seqlens, meta.m[li] if keep else None,
+                           meta.seq_slot if keep else None)
+    return y_l, OF.linear(_decay_branch(model, i, d, right, s), p[f"{i}.attn.o2.weight"])
+
+
+def _parallel_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, m_caches, cache_lens, slots):
+    c, p = model.config, model.p
+    b = c.blocks[i - 1]
+    w, d = b.wattn, b.decay
+    left, right = _parallel_split(b, OF.linear(h, p[f"{i}.attn.in.weight"]))
+    if w.rotary is not None:
+        attn_ops.rotate_qk_(left, w, cache_lens=cache_lens, slots=slots)
+    o = attn_ops.sink_window_decode_attention(left, w, None, None, k_caches[li], v_caches[li], cache_lens, slots, c.layer_norm_epsilon)
+    y_l = OF.linear(o, p[f"{i}.attn.o.weight"])
+    s = rec_ops.decay_step(rec_ops.decay_prepare(right, d, cache_lens=cache_lens, slots=slots), d, m_caches[li], slots)
+    return y_l, OF.linear(_decay_branch(model, i, d, right, s), p[f"{i}.attn.o2.weight"])
+
+
+def _finish_layer_block(model, i: int, b, x: torch.Tensor, y) -> None:
+    """"layer" stacks: x += mult * ls * LN_post(mixer output), then the feed-forward sublayer likewise.  `y` is the mixer's output,
+    or the pair of branch outputs of a `parallel` block (summed with `branch_scales` inside the norm kernel)."""
+    c, p = model.config, model.p
+    eps, mult = c.layer_norm_epsilon, c.residual_mult
+    y, y2 = y if isinstance(y, tuple) else (y, None)
+    sa, sb = b.branch_scales if y2 is not None else (1.0, 1.0)
+    h = OF.residual_add_centred_norm_(x, y, p[f"{i}.attn.ln_post.weight"], eps, p.get(f"{i}.attn.ls.weight"), mult, y2, sa, sb,
+                                      p[f"{i}.mlp.ln.weight"] if b.mlp is not None else None, model.dtype)
+    if b.mlp is not None:
+        OF.residual_add_centred_norm_(x, _mlp(model, i, h, b.mlp), p[f"{i}.mlp.ln_post.weight"], eps, p.get(f"{i}.mlp.ls.weight"), mult)
+
+
 def norm_offset(c) -> float:
     """What is added to a stored norm weight: 1 for weights stored around zero (`layer_norm_type` "gemma")."""
     return 1.0 if c.layer_norm_type == "gemma" else 0.0
@@ -265,6 +354,12 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta, pend
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     keep = meta.k is not None
+    if c.layer_norm_type == "layer":
+        h = OF.centred_norm(settle(model, x, pending), p[f"{i}.attn.ln.weight"], eps, model.dtype)
+        mixer = {"window_attention": _window_attention_packed, "delta": _delta_packed, "mlstm": _mlstm_packed, "latent_attention": _latent_rope_packed,
+                 "decay": _decay_packed, "parallel": _parallel_packed}[b.mixer]
+        _finish_layer_block(model, i, b, x, mixer(model, i, li, h, meta))
+        return x, None
     if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G, eps,
@@ -295,28 +390,39 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta, pend
     return x, None
 
 
+def _mixer_decode(model, b, i: int, li: int, h: torch.Tensor, k_caches, v_caches, m_caches, cache_lens, slots):
+    if b.mixer == "window_attention":
+        return _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
+    if b.mixer == "mlstm":
+        return _mlstm_decode(model, i, li, h, k_caches, v_caches, slots)
+    if b.mixer == "latent_attention":
+        return _latent_rope_decode(model, i, li, h, k_caches, cache_lens, slots)
+    if b.mixer == "decay":
+        return _decay_decode(model, i, li, h, k_caches, cache_lens, slots)
+    if b.mixer == "parallel":
+        return _parallel_decode(model, i, li, h, k_caches, v_caches, m_caches, cache_lens, slots)
+    return _delta_decode(model, i, li, h, k_caches, v_caches, slots)
+
+
 def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.Tensor], v_caches: List[torch.Tensor],
-                 cache_lens: torch.Tensor, slots: Optional[torch.Tensor], pending: Optional[torch.Tensor] = None, defer: bool = False):
+                 cache_lens: torch.Tensor, slots: Optional[torch.Tensor], pending: Optional[torch.Tensor] = None, defer: bool = False,
+                 m_caches: Optional[List[Optional[torch.Tensor]]] = None):
     """Block i for one new token per row; x [B, H] is updated in place.  Row b lives in state slot slots[b] (None: slot b).
     Returns (x, pending) as `block_packed` does."""
     c, p = model.config, model.p
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
+    if c.layer_norm_type == "layer":
+        h = OF.centred_norm(settle(model, x, pending), p[f"{i}.attn.ln.weight"], eps, model.dtype)
+        _finish_layer_block(model, i, b, x, _mixer_decode(model, b, i, li, h, k_caches, v_caches, m_caches, cache_lens, slots))
+        return x, None
     if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input_step(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G,
                                                                                             eps, None, None, slots, model.dtype,
                                                                                             w_offset=norm_offset(c))
-        if b.mixer == "window_attention":
-            y = _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
-        elif b.mixer == "mlstm":
-            y = _mlstm_decode(model, i, li, h, k_caches, v_caches, slots)
-        elif b.mixer == "latent_attention":
-            y = _latent_rope_decode(model, i, li, h, k_caches, cache_lens, slots)
-        else:
-            y = _delta_decode(model, i, li, h, k_caches, v_caches, slots)
-        return x, _finish_block(model, i, b, x, y, defer)
+        return x, _finish_block(model, i, b, x, _mixer_decode(model, b, i, li, h, k_caches, v_caches, m_caches, cache_lens, slots), defer)
     settle(model, x, pending)
     conv = v_caches[li] if c.conv_taps else None
     h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"),
@@ -336,6 +442,8 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
 def final_norm(model, x: torch.Tensor, pending: Optional[torch.Tensor] = None) -> torch.Tensor:
     c = model.config
     w = model.p[f"{c.n_layers}.ln_f.weight"]
+    if c.layer_norm_type == "layer":
+        return OF.centred_norm(settle(model, x, pending), w, c.layer_norm_epsilon, model.dtype)
     if pending is not None and plain_prenorm(c):
         return OF.add_rms_norm_(x, pending, w, c.layer_norm_epsilon, model.dtype, norm_offset(c))
     return OF.sublayer_input(settle(model, x, pending), w, c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype, w_offset=norm_offset(c))

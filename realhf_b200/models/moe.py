@@ -57,10 +57,10 @@ def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: O
             _, idx = torch.topk(sinkhorn(logits), mcfg.top_k, dim=-1)
         probs = torch.sigmoid(logits).gather(-1, idx) if mcfg.top_k == 1 else torch.softmax(logits, -1).gather(-1, idx)
         return probs, idx
-    if mcfg.routing_type == "softmax_all":
+    if mcfg.routing_type in ("softmax_all", "sigmoid"):
         if bias is None and _native_route(h, w_router, mcfg):
             return softmax_all_route(h, w_router, correction, mcfg)[:2]
-        full = torch.softmax(logits, dim=-1)
+        full = torch.sigmoid(logits) if mcfg.routing_type == "sigmoid" else torch.softmax(logits, dim=-1)
         idx = torch.topk(full + correction.float() if correction is not None else full, mcfg.top_k, dim=-1).indices
         probs = full.gather(-1, idx)
         return (probs / probs.sum(-1, keepdim=True) if mcfg.renormalize else probs), idx
@@ -87,11 +87,13 @@ def _native_route(h: torch.Tensor, w_router: torch.Tensor, mcfg) -> bool:
 
 def softmax_all_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], mcfg,
                       w_gate: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """One kernel for routing_type "softmax_all" (inference): fp32 logits W h, softmax over all outputs, the top_k largest of
-    score + correction, their scores as weights; with `w_gate` [1, H] also sigmoid(w_gate . h) per token ([T] fp32)."""
+    """One kernel for routing_type "softmax_all" / "sigmoid" (inference): fp32 logits W h, scores = softmax over all outputs (or the
+    sigmoid of every output), the top_k largest of score + correction, their scores as weights; with `w_gate` [1, H] also
+    sigmoid(w_gate . h) per token ([T] fp32)."""
     from realhf_b200.ops import lib
     probs, idx, gate = lib().softmax_router(h, w_router.contiguous(), correction.contiguous() if correction is not None else None,
-                                            w_gate.contiguous().view(-1) if w_gate is not None else None, mcfg.top_k, bool(mcfg.renormalize))
+                                            w_gate.contiguous().view(-1) if w_gate is not None else None, mcfg.top_k, bool(mcfg.renormalize),
+                                            mcfg.routing_type == "sigmoid")
     return probs, idx, (gate if w_gate is not None else None)
 
 
@@ -128,7 +130,7 @@ def grouped_mlp_device(x_sorted: torch.Tensor, counts_dev: torch.Tensor, w_gate_
     offsets = torch.zeros(counts_dev.numel() + 1, dtype=torch.int32, device=x_sorted.device)
     offsets[1:] = counts_dev.cumsum(0)
     h = G.grouped_linear(x_sorted, w_gate_up, offsets)
-    return G.grouped_linear(OF.gated_act(h, act), w_down, offsets)
+    return G.grouped_linear(_expert_act(h, act), w_down, offsets)
 
 
 def _use_grouped_kernel(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
@@ -146,20 +148,30 @@ def grouped_mlp(x_sorted: torch.Tensor, counts: List[int], w_gate_up: torch.Tens
         if n == 0:
             continue
         xe = x_sorted[off: off + n]
-        outs.append(OF.linear(OF.gated_act(OF.linear(xe, w_gate_up[e]), act), w_down[e]) if e < w_gate_up.shape[0] else xe)
+        outs.append(OF.linear(_expert_act(OF.linear(xe, w_gate_up[e]), act), w_down[e]) if e < w_gate_up.shape[0] else xe)
         off += n
     if not outs:
         return x_sorted.new_zeros(0, w_down.shape[1])
     return torch.cat(outs, 0)
 
 
-def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
+def _scaled_rows(h: torch.Tensor, tok: torch.Tensor, w_sorted: torch.Tensor) -> torch.Tensor:
+    """h[tok] * w (the routing weight on the expert's input): the product in fp32, stored in h's dtype."""
+    return (h.index_select(0, tok).float() * w_sorted.float().unsqueeze(-1)).to(h.dtype)
+
+
+def moe_forward(model, i: int, h: torch.Tensor, mcfg=None, clamp: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     """MoE MLP of block i on normalised hidden states h ([T, H], or [T/t, H] under sequence parallelism).  `mcfg`: the block's own
     MoE config in a heterogeneous stack (default: the model-wide one).  With `fp32_residual` the experts' outputs are combined
-    in fp32 and the result stays fp32."""
+    in fp32 and the result stays fp32.  `clamp` = (limit, alpha): the experts are clamped gated units, y = g sigmoid(alpha g) (u + 1)
+    with g = min(gate, limit), u = clamp(up, +-limit), instead of units gated by the model's activation.  With `mcfg.scale_input`
+    an assignment's routing weight multiplies the expert's input row and the outputs are summed unweighted."""
     c, ctx = model.config, model.ctx
     mcfg = mcfg if mcfg is not None else c.moe
     E, k = mcfg.num_experts, mcfg.top_k
+    act = c.activation_function if clamp is None else ("clamped", float(clamp[0]), float(clamp[1]))
+    if mcfg.scale_input or not mcfg.shared_gate:
+        assert mcfg.routing_type in ("softmax_all", "sigmoid") and ctx.tp_size == 1, "scale_input / ungated shared experts: single-rank stacks"
     w_gu, w_dn = model.p[f"{i}.mlp.experts.gate_up.weight"], model.p[f"{i}.mlp.experts.down.weight"]
     ep = mcfg.expert_parallel and ctx.tp_size > 1
     sp = model.sequence_parallel
@@ -171,11 +183,11 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         h = TP.copy_to_tp(h, ctx)
     T, H = h.shape
     gate_sh = None
-    fused = (mcfg.routing_type == "softmax_all" and model.p.get(f"{i}.mlp.router.bias") is None and not ep and ctx.tp_size == 1
+    fused = (mcfg.routing_type in ("softmax_all", "sigmoid") and model.p.get(f"{i}.mlp.router.bias") is None and not ep and ctx.tp_size == 1
              and mcfg.capacity_factor is None and _native_route(h, model.p[f"{i}.mlp.router.weight"], mcfg))
     if fused:       # routing, the shared expert's gate and (below) the weighted sum of the experts' outputs: one kernel each
         probs, idx, gate_sh = softmax_all_route(h, model.p[f"{i}.mlp.router.weight"], model.p.get(f"{i}.mlp.router.correction"), mcfg,
-                                                model.p[f"{i}.mlp.shared.sg.weight"] if mcfg.shared_ff else None)
+                                                model.p[f"{i}.mlp.shared.sg.weight"] if mcfg.shared_ff and mcfg.shared_gate else None)
     else:
         probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"),
                            model.p.get(f"{i}.mlp.router.correction"))
@@ -187,16 +199,21 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         # counting kernel instead of a sort; rows of identity experts lie behind the last offset and never enter the GEMMs
         from realhf_b200.ops import gemm as G, lib
         back, offsets = lib().moe_dispatch(idx, E, E + n_id)
-        hid = G.grouped_linear(lib().moe_gather(h, back, k), w_gu, offsets)
-        y_sorted = G.grouped_linear(OF.gated_act(hid, c.activation_function), w_dn, offsets)
+        hid = G.grouped_linear(lib().moe_gather(h, back, k, probs if mcfg.scale_input else None), w_gu, offsets)
+        y_sorted = G.grouped_linear(_expert_act(hid, act), w_dn, offsets)
         out = torch.empty(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
-        lib().moe_combine(y_sorted, h, back, probs, idx, _shared_mlp(model, i, h) if mcfg.shared_ff else None, gate_sh, out, E)
+        lib().moe_combine(y_sorted, h, back, probs, idx, _shared_mlp(model, i, h, mcfg, act) if mcfg.shared_ff else None, gate_sh, out, E,
+                          bool(mcfg.scale_input))
         return out
     probs = _apply_capacity(probs, idx, E, mcfg)
     flat_e = idx.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
     tok = torch.arange(T, device=h.device).repeat_interleave(k)[order]
     w_sorted = probs.reshape(-1)[order]
+    if mcfg.scale_input:
+        assert not ep and not n_id, "scale_input: local experts, no identity experts"
+        x_scaled = _scaled_rows(h, tok, w_sorted)
+        w_sorted = torch.ones_like(w_sorted)
     if ep and sp:
         from realhf_b200.parallel import ep as EP
         x_sorted = h.index_select(0, tok)
@@ -244,7 +261,7 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         out = torch.zeros(T, H, dtype=h.dtype, device=h.device).index_add_(
             0, tok[sel], (y_sorted * w_sorted[sel].to(y_sorted.dtype).unsqueeze(-1)).to(h.dtype))
         return TP.reduce_from_tp(out, ctx)
-    x_sorted = h.index_select(0, tok)
+    x_sorted = x_scaled if mcfg.scale_input else h.index_select(0, tok)
     grouped = mcfg.use_grouped_gemm and _use_grouped_kernel(x_sorted, w_gu, w_dn)   # use_grouped_gemm=False: one GEMM pair per expert
     if not grouped and h.is_cuda and torch.cuda.is_current_stream_capturing():
         # operands the grouped kernel does not take (fp32) inside a CUDA-graph capture, where the per-expert loop's host read of
@@ -253,25 +270,29 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         gate = torch.zeros(T, E + n_id, dtype=torch.float32, device=h.device).scatter_(1, idx, probs.float())
         out = torch.zeros(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
         for e in range(E):
+            if mcfg.scale_input:       # expert(w h) where chosen (w > 0), nothing elsewhere
+                y = OF.linear(_expert_act(OF.linear((h.float() * gate[:, e: e + 1]).to(h.dtype), w_gu[e]), act), w_dn[e])
+                out += (y.float() * (gate[:, e: e + 1] > 0)).to(out.dtype)
+                continue
             y = OF.linear(OF.gated_act(OF.linear(h, w_gu[e]), c.activation_function), w_dn[e])
             out += (y.float() * gate[:, e: e + 1]).to(out.dtype)
         if n_id:
             out += (h.float() * gate[:, E:].sum(1, keepdim=True)).to(out.dtype)
-        return _add_shared(model, i, h, mcfg, out)
+        return _add_shared(model, i, h, mcfg, out, act)
     if grouped:
         # the device-side offsets end at expert E: rows of identity experts (sorted last) are not touched by the GEMMs and pass through
-        y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E + n_id)[:E], w_gu, w_dn, c.activation_function)
+        y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E + n_id)[:E], w_gu, w_dn, act)
         if n_id and not fused:
             y_sorted = torch.where((flat_e[order] >= E).unsqueeze(-1), x_sorted, y_sorted)
     else:
         counts = torch.bincount(flat_e, minlength=E + n_id).tolist()
-        y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, c.activation_function)
+        y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, act)
     if fused:
         from realhf_b200.ops import lib
         back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
         out = torch.empty(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
-        lib().moe_combine(y_sorted.contiguous(), h, back, probs.float().contiguous(), idx, _shared_mlp(model, i, h) if mcfg.shared_ff else None, gate_sh,
-                          out, E)
+        lib().moe_combine(y_sorted.contiguous(), h, back, probs.float().contiguous(), idx,
+                          _shared_mlp(model, i, h, mcfg, act) if mcfg.shared_ff else None, gate_sh, out, E, bool(mcfg.scale_input))
         return out
     if c.fp32_residual:
         # fp32 combine in a fixed order (an atomic index_add_ would make the sum depend on the run): rows back to (token, choice)
@@ -282,17 +303,30 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
         out = torch.zeros(T, H, dtype=y_sorted.dtype, device=h.device).index_add_(0, tok, y_sorted * w_sorted.to(y_sorted.dtype).unsqueeze(-1))
     if ctx.tp_size > 1:  # experts are F-sharded over TP: partial sums
         out = TP.reduce_scatter_to_sp(out, ctx) if sp else TP.reduce_from_tp(out, ctx)
-    return _add_shared(model, i, h, mcfg, out)
+    return _add_shared(model, i, h, mcfg, out, act)
 
 
-def _add_shared(model, i: int, h: torch.Tensor, mcfg, out: torch.Tensor) -> torch.Tensor:
-    """out += shared expert(h) * sigmoid(w_sg . h): an expert every token uses, scaled by one learned gate value per token (fp32)."""
+def _expert_act(hid: torch.Tensor, act) -> torch.Tensor:
+    """The experts' gated activation on the fused [.., 2F] gate | up rows: the named activation, or ("clamped", limit, alpha)."""
+    if isinstance(act, tuple):
+        return OF.clamped_glu(hid, act[1], act[2])
+    return OF.gated_act(hid, act)
+
+
+def _add_shared(model, i: int, h: torch.Tensor, mcfg, out: torch.Tensor, act=None) -> torch.Tensor:
+    """out += shared expert(h) * sigmoid(w_sg . h): an expert every token uses, scaled by one learned gate value per token (fp32;
+    `shared_gate` False: added unscaled)."""
     if not mcfg.shared_ff:
         return out
-    g = torch.sigmoid(F.linear(h.float(), model.p[f"{i}.mlp.shared.sg.weight"].float()))
-    return out + (_shared_mlp(model, i, h).float() * g).to(out.dtype)
+    y = _shared_mlp(model, i, h, mcfg, act).float()
+    if mcfg.shared_gate:
+        y = y * torch.sigmoid(F.linear(h.float(), model.p[f"{i}.mlp.shared.sg.weight"].float()))
+    return out + y.to(out.dtype)
 
 
-def _shared_mlp(model, i: int, h: torch.Tensor) -> torch.Tensor:
+def _shared_mlp(model, i: int, h: torch.Tensor, mcfg=None, act=None) -> torch.Tensor:
     p = model.p
+    if isinstance(act, tuple):     # clamped unit with the shared expert's own limit
+        limit = mcfg.shared_limit if mcfg is not None and mcfg.shared_limit is not None else act[1]
+        return OF.linear(OF.clamped_gated_linear(h, p[f"{i}.mlp.shared.gate_up.weight"], limit, act[2]), p[f"{i}.mlp.shared.down.weight"])
     return OF.linear(OF.gated_linear(h, p[f"{i}.mlp.shared.gate_up.weight"], model.config.activation_function), p[f"{i}.mlp.shared.down.weight"])

@@ -368,6 +368,8 @@ class ReaLModel(nn.Module):
             x = x * torch.tensor(c.hidden_dim ** 0.5, dtype=x.dtype, device=x.device)
         if c.fp32_residual:
             x = x.float()
+        if c.embed_scale is not None:
+            x = x * torch.tensor(c.embed_scale, dtype=x.dtype, device=x.device)
         return self._dropout(x, c.embd_pdrop)
 
     # ------------------------------------------------------------------ dropout under tensor parallelism
@@ -662,11 +664,13 @@ class ReaLModel(nn.Module):
     # ------------------------------------------------------------------ decode step (one token per sequence)
     @torch.no_grad()
     def decode_step(self, input_ids: Optional[torch.Tensor], k_caches: List[torch.Tensor], v_caches: List[torch.Tensor],
-                    cache_lens: torch.Tensor, hidden: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    cache_lens: torch.Tensor, hidden: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                    m_caches: Optional[List[Optional[torch.Tensor]]] = None) -> torch.Tensor:
         """input_ids [B] -> final hidden [B, H] (last stage: after ln_f).  Appends K/V at `cache_lens` in place.
         Caches: one [B, S, nkv_local, hd] tensor per local block.  Capturable in a CUDA graph (no host sync).
         Heterogeneous stacks: the caches are the per-block state tensors of `DecodeState` (see models/hetero_block.py) and
-        `slots` [B] int32 names the state slot of every row (None: row b is slot b; `cache_lens` is indexed by slot)."""
+        `slots` [B] int32 names the state slot of every row (None: row b is slot b; `cache_lens` is indexed by slot); `m_caches`
+        is `DecodeState.m`, the third state tensor of the blocks that hold one."""
         c = self.config
         if c.blocks is not None:
             from realhf_b200.models import hetero_block as HB
@@ -680,7 +684,7 @@ class ReaLModel(nn.Module):
                     pend = None
                 elif x is x0 and c.loop is not None:
                     x = x0.clone()
-                x, pend = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots, pend, defer=True)
+                x, pend = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots, pend, defer=True, m_caches=m_caches)
             if c.n_layers in self.layers:
                 return HB.final_norm(self, x, pend)
             return HB.settle(self, x, pend)

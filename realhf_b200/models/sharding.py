@@ -127,6 +127,11 @@ def delta_sections(d) -> Tuple[int, ...]:
     return (d.n_kv_heads * d.qk_dim, d.n_kv_heads * d.qk_dim, d.n_heads * d.v_dim, d.n_heads * d.v_dim, _pad8(2 * d.n_heads))
 
 
+def decay_sections(d) -> Tuple[int, ...]:
+    """Rows of the fused input projection of a decayed-linear-attention mixer: [q | k | v | output gate]."""
+    return (d.n_heads * d.qk_dim, d.n_heads * d.qk_dim, d.n_heads * d.v_dim, d.n_heads * d.v_dim)
+
+
 def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSpec]:
     """Specs of block `layer_idx` of a heterogeneous stack (`cfg.blocks`).  Projections that read the same input are one tensor
     made of sections: `attn.q_dkv` = [queries | latent down-projection] (the second section is absent in a block that reads
@@ -145,7 +150,20 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
     add("attn.ln.weight", (H,), None, init=norm_init)
     if cfg.conv_taps:
         add("attn.canon.weight", (H, cfg.conv_taps), None)
-    if b.mixer == "window_attention":
+    if b.mixer in ("decay", "parallel"):
+        # one projection for everything that reads the mixer's input: [window attention q | k | v] (mixer "parallel" only), then the
+        # decayed linear attention's [q | k | v | gate]; each branch has its own output projection
+        d = b.decay
+        sec = (wattn_sections(b.wattn) if b.mixer == "parallel" else ()) + decay_sections(d)
+        add("attn.in.weight", (sum(sec), H), None, sec)
+        if d.out_norm == "full":
+            add("attn.o_norm.weight", (d.n_heads * d.v_dim,), None, init="ones")
+        if b.mixer == "parallel":
+            add("attn.o.weight", (H, b.wattn.n_heads * b.wattn.v_dim), None)
+            add("attn.o2.weight", (H, d.n_heads * d.v_dim), None)
+        else:
+            add("attn.o.weight", (H, d.n_heads * d.v_dim), None)
+    elif b.mixer == "window_attention":
         w = b.wattn
         sec = wattn_sections(w)
         add("attn.qkvg.weight", (sum(sec), H), None, sec)
@@ -200,6 +218,8 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
         add("attn.o.weight", (H, a.n_heads * a.v_dim), None)
     if cfg.sandwich_norm:
         add("attn.ln_post.weight", (H,), None, init="ones")
+    if cfg.layer_scale:
+        add("attn.ls.weight", (H,), None, init="ones")
     if b.mlp is not None:
         F = b.mlp.ff
         add("mlp.ln.weight", (H,), None, init=norm_init)
@@ -208,7 +228,7 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
         if b.mlp.kind == "moe":
             mo = b.mlp.moe
             E = mo.num_experts
-            if mo.routing_type == "softmax_all":
+            if mo.routing_type in ("softmax_all", "sigmoid"):
                 add("mlp.router.weight", (mo.n_router_outputs, H), None)
                 if mo.score_correction:
                     add("mlp.router.correction", (mo.n_router_outputs,), None, init="zeros")
@@ -220,7 +240,8 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
             if mo.shared_ff:
                 add("mlp.shared.gate_up.weight", (2 * mo.shared_ff, H), None, (mo.shared_ff, mo.shared_ff))
                 add("mlp.shared.down.weight", (H, mo.shared_ff), None)
-                add("mlp.shared.sg.weight", (1, H), None)
+                if mo.shared_gate:
+                    add("mlp.shared.sg.weight", (1, H), None)
         elif b.mlp.kind == "relu2":
             add("mlp.up.weight", (F, H), None)
             add("mlp.down.weight", (H, F), None)
@@ -229,6 +250,8 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
             add("mlp.down.weight", (H, F), None)
         if cfg.sandwich_norm:
             add("mlp.ln_post.weight", (H,), None, init="ones")
+        if cfg.layer_scale:
+            add("mlp.ls.weight", (H,), None, init="ones")
     if layer_idx == cfg.n_layers:
         add("ln_f.weight", (H,), None, init=norm_init)
     return out

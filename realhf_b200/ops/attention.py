@@ -382,6 +382,28 @@ def value_norm_store(qkvg, a, eps: float, k_cache, v_cache, tok_slot, pos, remai
     return value_norm_store_ref(qkvg, a, eps, k_cache, v_cache, tok_slot, pos, remain)
 
 
+def rotate_qk_(qkv, a, pos=None, cache_lens=None, slots=None):
+    """In place: the (n_heads + n_kv_heads) query / key heads at the start of every row of `qkv` [T, ld] are rotated by the row's
+    position over the first `a.rotary.dims` dimensions (angle = position * f_i as an fp32 product, exact sin / cos; the rotated
+    values are stored in the tensor's dtype).  Packed form: `pos` [T] int32; step form (`pos` None): row b's position is
+    cache_lens[slots[b]] (slots None: cache_lens[b]).  Keys are therefore cached rotated."""
+    rot = a.rotary
+    inv_freq = rotary_table(rot, qkv.device)[0]
+    n_h = a.n_heads + a.n_kv_heads
+    if use_native(qkv):
+        lib().rotate_heads_(qkv, pos, cache_lens if pos is None else None, slots if pos is None else None, inv_freq, n_h, a.qk_dim, rot.dims,
+                            bool(rot.interleaved))
+        return qkv
+    from realhf_b200.ops.recurrent import _rotate_heads_ref
+    T = qkv.shape[0]
+    if pos is None:
+        idx = slots.long() if slots is not None else torch.arange(T, device=qkv.device)
+        pos = cache_lens[idx]
+    x = qkv[:, : n_h * a.qk_dim].float().reshape(T, n_h, a.qk_dim)
+    qkv[:, : n_h * a.qk_dim] = _rotate_heads_ref(x, pos, rot, inv_freq).reshape(T, -1).to(qkv.dtype)
+    return qkv
+
+
 def _sink_softmax_pv(s, ok, sink_h, v):
     """fp32 scores s [Lq, Lk], visibility ok, sink logit (tensor scalar or None) -> softmax-with-sink weights @ v."""
     s = s.masked_fill(~ok, float("-inf"))

@@ -698,6 +698,41 @@ def residual_add_norm_(x, y, w, groups: int, eps: float):
     return x
 
 
+def centred_norm_ref(x, w, eps: float):
+    """fp32 LayerNorm without a bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w."""
+    x = x.float()
+    mu = x.mean(-1, keepdim=True)
+    dx = x - mu
+    return dx * torch.rsqrt(dx.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+
+def centred_norm(x, w, eps: float, out_dtype):
+    """Bias-free LayerNorm of every row of x [T, W] (fp32 statistics, the variance as the mean of the squared deviations), times w,
+    in out_dtype."""
+    if use_native(x):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().centred_norm(None, x.contiguous(), None, 1.0, 1.0, None, None, 1.0, w, out, eps)
+        return out
+    return centred_norm_ref(x, w, eps).to(out_dtype)
+
+
+def residual_add_centred_norm_(x, y, w, eps: float, scale=None, mult: float = 1.0, y2=None, a: float = 1.0, b: float = 1.0, next_w=None,
+                               out_dtype=None):
+    """x += mult * scale * LayerNorm(a y + b y2) * w in place (bias-free LayerNorm; `scale` a vector or None; y2 None: the branch
+    output is a y), the sum formed in fp32 and stored in x's dtype.  With `next_w`, also returns LayerNorm(x) * next_w of the
+    updated row in out_dtype (the next sublayer's input), from the same kernel."""
+    if use_native(x) and x.is_contiguous():
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if next_w is not None else None
+        lib().centred_norm(x, y.contiguous(), y2.contiguous() if y2 is not None else None, a, b, w, scale, mult, next_w, out, eps)
+        return out
+    br = a * y.float() + (b * y2.float() if y2 is not None else 0.0)
+    n = centred_norm_ref(br, w, eps)
+    if scale is not None:
+        n = n * scale.float()
+    x.copy_((x.float() + mult * n).to(x.dtype))
+    return centred_norm_ref(x, next_w, eps).to(out_dtype) if next_w is not None else None
+
+
 def clamped_glu_ref(gu, limit: float, alpha: float):
     F_ = gu.shape[-1] // 2
     g = gu[..., :F_].float().clamp(max=limit)

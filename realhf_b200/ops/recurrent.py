@@ -264,3 +264,128 @@ def mlstm_out(o, m, w, gate, eps: float, out_dtype):
     h = o[..., :dv] / den.unsqueeze(-1)
     h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
     return (h.reshape(T, H * dv) * w.float() * torch.sigmoid(gate[:, : H * dv].float())).to(out_dtype)
+
+
+# ------------------------------------------------------------------------------------------------ decayed linear attention
+# (`DecayConfig`: retention, lightning attention).  Per head, with a matrix state S [d, dv] in fp32 and a constant decay g_h:
+#   S_t = g_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t          (no softmax, no denominator)
+# The stages, each = PyTorch reference + sm_100a kernel (`csrc/decay.cu`):
+#   decay_prepare   the projection row [q (H d) | k (H d) | v (H dv) | gate (H dv)] -> fp32 `u` [T, 2 H d + H dv] = [q | k | v]: SiLU on
+#                   all three (`act`), or the rotation of q and k by the position (angles and products in fp32) and `k_scale` on k
+#   decay_scan      the recurrence over every packed sequence from S = 0, or one token per row against the slots' states
+#   decay_out       the output norm (per head without a weight, or over all heads with one), times silu / sigmoid of the gate
+
+
+def decay_table(d, device) -> torch.Tensor:
+    """fp32 [H] decays on `device` (cached on the config object)."""
+    hit = getattr(d, "_decay_dev", None)
+    if hit is None or hit.device != torch.device(device):
+        hit = torch.tensor(d.decay, dtype=torch.float64).float().to(device)
+        d._decay_dev = hit
+    return hit
+
+
+def _rotate_heads_ref(x, p, rot, inv_freq):
+    """x [T, H, d] fp32: the first rot.dims dimensions of every head turn by p * f_i; pairs (i, i + dims / 2) or (2i, 2i + 1)."""
+    n = rot.dims
+    ang = p.float().unsqueeze(-1) * inv_freq                 # fp32 product, as the kernels form it
+    cs, sn = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+    out = x.clone()
+    if rot.interleaved:
+        a, b = x[..., 0:n:2], x[..., 1:n:2]
+        out[..., 0:n:2] = a * cs - b * sn
+        out[..., 1:n:2] = b * cs + a * sn
+    else:
+        a, b = x[..., : n // 2], x[..., n // 2:n]
+        out[..., : n // 2] = a * cs - b * sn
+        out[..., n // 2:n] = b * cs + a * sn
+    return out
+
+
+def decay_prepare(proj, d, pos=None, cache_lens=None, slots=None):
+    """proj [T, >= d.width] (a view with its own row stride is fine) -> fp32 u [T, 2 H d + H dv].  Packed form: `pos` [T] int32; step
+    form (`pos` None): row b's position is cache_lens[slots[b]] (slots None: cache_lens[b])."""
+    from realhf_b200.ops.attention import rotary_table
+    T = proj.shape[0]
+    H, dk, dv = d.n_heads, d.qk_dim, d.v_dim
+    nq, nv = H * dk, H * dv
+    inv_freq = rotary_table(d.rotary, proj.device)[0] if d.rotary is not None else None
+    if use_native(proj):
+        u = torch.empty(T, 2 * nq + nv, dtype=torch.float32, device=proj.device)
+        lib().decay_prepare(proj, u, pos, cache_lens if pos is None else None, slots if pos is None else None, inv_freq, H, dk, dv,
+                            d.rotary.dims if d.rotary is not None else 0, bool(d.rotary.interleaved) if d.rotary is not None else False,
+                            d.act == "silu", float(d.k_scale))
+        return u
+    x = proj[:, : 2 * nq + nv].float()
+    if d.act == "silu":
+        x = F.silu(x)
+    q, k, v = x[:, :nq].reshape(T, H, dk), x[:, nq:2 * nq].reshape(T, H, dk), x[:, 2 * nq:]
+    if d.rotary is not None:
+        if pos is None:
+            idx = slots.long() if slots is not None else torch.arange(T, device=proj.device)
+            p = cache_lens[idx]
+        else:
+            p = pos
+        q, k = _rotate_heads_ref(q, p, d.rotary, inv_freq), _rotate_heads_ref(k, p, d.rotary, inv_freq)
+    k = k * torch.tensor(d.k_scale, dtype=torch.float32)
+    return torch.cat([q.reshape(T, nq), k.reshape(T, nq), v], -1)
+
+
+def _decay_ref(u, d, seqs, state, slot_of, load_state):
+    T = u.shape[0]
+    H, dk, dv = d.n_heads, d.qk_dim, d.v_dim
+    nq = H * dk
+    q, k, v = u[:, :nq].view(T, H, dk), u[:, nq:2 * nq].view(T, H, dk), u[:, 2 * nq:].view(T, H, dv)
+    g = decay_table(d, u.device).view(H, 1, 1)
+    o = torch.empty(T, H, dv, dtype=torch.float32, device=u.device)
+    for n, (s0, e0) in enumerate(seqs):
+        if e0 == s0:
+            continue
+        sl = slot_of(n)
+        S = state[sl].clone() if load_state else torch.zeros(H, dk, dv, dtype=torch.float32, device=u.device)
+        for t in range(s0, e0):
+            S = g * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        if state is not None:
+            state[sl] = S
+    return o
+
+
+def decay_scan(u, d, cu_seqlens, state=None, seq_slot=None, load_state: bool = False):
+    """Packed recurrence over every sequence from S = 0 (or, with `load_state`, from the slot's state); the final state is left in
+    state[seq_slot[n]] ([n_slots, H, d, dv] fp32) when `state` is given.  Returns o [T, H, dv] fp32."""
+    T = u.shape[0]
+    if use_native(u) and d.qk_dim <= 1024:
+        o = torch.empty(T, d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+        lib().decay_scan(u, decay_table(d, u.device), o, cu_seqlens, state, seq_slot if state is not None else None, d.n_heads, d.qk_dim,
+                         d.v_dim, bool(load_state))
+        return o
+    cu = cu_seqlens.tolist()
+    return _decay_ref(u, d, list(zip(cu[:-1], cu[1:])), state, lambda n: int(seq_slot[n]) if seq_slot is not None else n, load_state)
+
+
+def decay_step(u, d, state, slots=None):
+    """One token per row against state[slots[b]] (slots None: row b is slot b), updated in place.  Returns o [B, H, dv] fp32."""
+    B = u.shape[0]
+    if use_native(u) and d.qk_dim <= 1024:
+        o = torch.empty(B, d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+        lib().decay_scan(u, decay_table(d, u.device), o, None, state, slots, d.n_heads, d.qk_dim, d.v_dim, True)
+        return o
+    return _decay_ref(u, d, [(b, b + 1) for b in range(B)], state, lambda n: int(slots[n]) if slots is not None else n, True)
+
+
+def decay_out(o, d, w, gate, eps: float, out_dtype):
+    """o [T, H, dv] fp32 -> [T, H * dv] in out_dtype: o / rms(o) per head (`out_norm` "head") or over all heads times w [H * dv]
+    ("full"), then times silu(gate) or sigmoid(gate) (`gate` [T, >= H * dv], any row stride)."""
+    T, H, dv = o.shape
+    if use_native(o):
+        out = torch.empty(T, H * dv, dtype=out_dtype, device=o.device)
+        lib().decay_out(o, w if d.out_norm == "full" else None, gate, out, eps, d.out_norm == "full", d.gate == "silu")
+        return out
+    if d.out_norm == "full":
+        h = o.reshape(T, H * dv)
+        h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    else:
+        h = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, H * dv)
+    g = gate[:, : H * dv].float()
+    return (h * (F.silu(g) if d.gate == "silu" else torch.sigmoid(g))).to(out_dtype)
