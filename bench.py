@@ -315,7 +315,7 @@ def main():
     ap.add_argument("--gen-fp8", action="store_true",
                     help="NOT the headline precision: decode with e4m3 weights / activations (GenerationHyperparameters.fp8_weights); "
                          "the JSON line is labelled and carries no vs_baseline")
-    ap.add_argument("--serve-bench", default="", choices=["", "rapodra", "tizodra", "defilorn"],
+    ap.add_argument("--serve-bench", default="", choices=["", "rapodra", "tizodra", "defilorn", "buvesun"],
                     help="NOT the headline workload: prefill / decode throughput of the named heterogeneous-stack design next to a LLaMA of "
                          "equal size, and the roofline position of its kernels (one JSON line per result; 1 GPU)")
     ap.add_argument("--serve-sizes", default="", help="--serve-bench only: comma-separated size names (default: all)")

@@ -1,6 +1,8 @@
 """Prefill / decode throughput of a heterogeneous-stack design next to the closest homogeneous model of equal size, and the
 roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra`,
-`--serve-bench tizodra` or `--serve-bench defilorn` (the default workload of bench.py is unaffected).
+`--serve-bench tizodra`, `--serve-bench defilorn` or `--serve-bench buvesun` (the default workload of bench.py is unaffected).
+Buvesun is also timed beside a Defilorn of equal size, the closest heterogeneous stack (window attention, a matrix-state mixer, routed
+feed-forwards with a shared expert).
 
 Both models run through `models.generation`: prefill = `prefill_into_state` (the packed prefill `generate` performs) into a
 standing decode state, decode = the CUDA-graph loop of `generate` with the sampler in the graph; random weights, bf16.  Timing: CUDA events, >= 3 warm-up calls, weights + state far larger than L2 per call for
@@ -79,13 +81,46 @@ def defilorn_config(s: dict, n_layers: int = 4) -> dict:
                 width=s["width"])
 
 
+BUVESUN_SIZES = {
+    # the Defilorn sizes (so that a Defilorn of equal size can be built beside it) plus: heads of the decayed linear attention,
+    # rotated dimensions, clamp limits
+    "1b-like": dict(DEFILORN_SIZES["1b-like"], r_heads=16, rot_dims=64, limit=7.0),
+    "7b-like": dict(DEFILORN_SIZES["7b-like"], r_heads=32, rot_dims=64, limit=7.0),
+}
+
+
+def buvesun_config(s: dict, n_layers: int = 4) -> dict:
+    """Parallel blocks (window attention beside lightning attention) and retention blocks in turn, every block with a routed
+    feed-forward and a shared expert; the first two blocks in a loop of one pass (so the re-injection projection is on the path)."""
+    H = s["r_heads"]
+    decay = [1.0 - 2.0 ** (-4.0 - 4.0 * h / max(H - 1, 1)) for h in range(H)]
+    moe = dict(kind="moe", expert=dict(ff=s["eff"], limit=s["limit"]), router=dict(experts=s["experts"], top=s["top"]),
+               shared=dict(ff=s["sff"], limit=s["limit"]))
+    par = dict(type="parallel", mlp=moe,
+               mixer=dict(left=dict(dim=s["dim"], heads=s["heads"], kv_heads=s["kv_heads"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+                                    mask=dict(size=s["window"]), rot=dict(base=5e5, dims=s["rot_dims"])), left_scale=0.6,
+                          right=dict(decay=decay, dim=s["dim"], heads=H, vdim=s["vdim"]), right_scale=1.1))
+    ret = dict(type="retention", mlp=moe, mixer=dict(decay=decay, dim=s["dim"], heads=H, vdim=s["vdim"], rot=dict(base=1e5, dims=s["dim"])))
+    layers = [par if i % 2 == 0 else ret for i in range(n_layers)]
+    return dict(architecture="Buvesun", embedding=dict(scale=2.0), layers=layers, loop=dict(start=0, stop=min(2, n_layers), times=1),
+                norm=dict(eps=1e-5), residual_mult=0.7, vocab=s["vocab"], width=s["width"])
+
+
+def _hetero_model(design: str, s: dict, n_layers: int, dev):
+    from realhf_b200.models import hf_io
+    from realhf_b200.models.real_model import ReaLModel
+    cfg = {"rapodra": rapodra_config, "tizodra": tizodra_config, "defilorn": defilorn_config, "buvesun": buvesun_config}[design](s, n_layers)
+    m = ReaLModel(hf_io.family(design).config_from_dict(cfg, False), dtype=torch.bfloat16, device=dev).init_random_fast()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    return m.eval()
+
+
 def _models(s: dict, n_layers: int, dev, design: str = "rapodra"):
     from realhf_b200.api.model import ReaLModelConfig
     from realhf_b200.models import hf_io
     from realhf_b200.models.real_model import ReaLModel
-    cfg = {"rapodra": rapodra_config, "tizodra": tizodra_config, "defilorn": defilorn_config}[design](s, n_layers)
-    rc = hf_io.family(design).config_from_dict(cfg, False)
-    new = ReaLModel(rc, dtype=torch.bfloat16, device=dev).init_random_fast()
+    new = _hetero_model(design, s, n_layers, dev)
     lc = ReaLModelConfig(n_layers=n_layers, n_kv_heads=s.get("kv_heads", s["heads"]), n_q_heads=s["heads"], hidden_dim=s["width"], intermediate_dim=s["ff"],
                          vocab_size=s["vocab"], head_dim=s["dim"], n_positions=8192, embd_pdrop=0.0, resid_pdrop=0.0, attn_pdrop=0.0,
                          activation_function="silu", scale_attn_by_inverse_layer_idx=False, use_attention_bias=False,
@@ -124,7 +159,10 @@ def model_numbers(name: str, s: dict, n_layers: int, batch: int, prompt_len: int
     g = GenerationHyperparameters(max_new_tokens=new_tokens, min_new_tokens=new_tokens, greedy=True, use_cuda_graph=True)
     ids = torch.randint(3, s["vocab"], (batch * prompt_len,), device=dev)
     cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
-    for label, m in ((design, new), ("llama-equal-size", old)):
+    arms = [(design, new), ("llama-equal-size", old)]
+    if design == "buvesun":
+        arms.insert(1, ("defilorn-equal-size", _hetero_model("defilorn", s, n_layers, dev)))
+    for label, m in arms:
         # prefill: the packed prefill into a standing decode state (`prefill_into_state`, what `generate` calls), so that the
         # number is the model's and not the caching allocator's (a fresh multi-GB state per `generate` call can fall into
         # cudaMalloc inside the timed region); decode: the CUDA-graph loop of `generate`
@@ -151,7 +189,7 @@ def model_numbers(name: str, s: dict, n_layers: int, batch: int, prompt_len: int
                         prefill_ms=round(pre_ms, 3), prefill_tokens_per_s=round(batch * prompt_len / pre_ms * 1e3),
                         decode_ms_per_step=round(dec_ms, 4), decode_tokens_per_s=round(batch / dec_ms * 1e3), dtype="bf16", data="synthetic",
                         params=sum(p.numel() for p in m.parameters())))
-    del new, old
+    del new, old, arms, m
     torch.cuda.empty_cache()
     return out
 
@@ -463,8 +501,139 @@ def defilorn_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx
     return rows
 
 
+def buvesun_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx: int, dev, peaks: Dict[str, float]) -> List[dict]:
+    """The Buvesun kernels next to the like kernels of the closest models at the same token count and head sizes: Defilorn's
+    matrix-memory LSTM and fused add + norm, its router and combination, LLaMA's rotation and attention.  Attention FLOPs count the
+    visible (query, key) pairs; the fp32 recurrences are held against the nominal fp32 CUDA-core rate or their bytes, whichever is
+    slower."""
+    from realhf_b200.models import hf_io
+    from realhf_b200.models.hetero_block import packed_meta
+    from realhf_b200.ops import attention as A
+    from realhf_b200.ops import functional as OF
+    from realhf_b200.ops import lib
+    from realhf_b200.ops import recurrent as RC
+    bf = torch.bfloat16
+    rc = hf_io.family("buvesun").config_from_dict(buvesun_config(s, 2), False)
+    wa, lt, rt = rc.blocks[0].wattn, rc.blocks[0].decay, rc.blocks[1].decay
+    ml = hf_io.family("defilorn").config_from_dict(defilorn_config(s, 3), False).blocks[1].mlstm
+    W, H, G, d, dv, win, HR = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], s["r_heads"]
+    T = batch * prompt_len
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_tflops = 148 * 128 * 2 * 1.9e9 / 1e12
+    rows = []
+
+    def add(kernel, like, ms, nbytes, flops, simt_fp32=False):
+        peak = fp32_tflops if simt_fp32 else peaks["bf16_tflops"]
+        floor_ms = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peak * 1e12)) * 1e3
+        rows.append(dict(bench="kernel", size=name, kernel=kernel, like=like, ms=round(ms, 4), gbytes=round(nbytes / 1e9, 4),
+                         gflop=round(flops / 1e9, 2), roofline_ms=round(floor_ms, 4), frac_of_measured_roofline=round(floor_ms / ms, 4),
+                         flop_peak="fp32 CUDA cores (nominal)" if simt_fp32 else "bf16 tensor (measured)"))
+
+    cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
+    slots = torch.arange(batch, dtype=torch.int32, device=dev)
+    meta = packed_meta(cu, T, slots, None, prompt_len)
+    x32 = torch.randn(T, W, device=dev)
+    xb, yb = x32.to(bf), torch.randn(T, W, device=dev).to(bf)
+    w = torch.ones(W, device=dev, dtype=bf)
+    # ---- row-wise
+    add("centred_norm (LayerNorm of the fp32 stream, prefill)", False, _time(lambda: OF.centred_norm(x32, w, 1e-5, bf), 10, flush=flush), T * W * 6, 0)
+    add("residual_add_centred_norm_ (two branches, output norm, layer scale, add, next norm; prefill)", False,
+        _time(lambda: OF.residual_add_centred_norm_(x32, xb, w, 1e-5, w, 0.7, yb, 0.6, 1.1, w, bf), 10, flush=flush), T * W * 14, 0)
+    add("add_rms_norm_ (defilorn: fp32 stream += branch, next norm; prefill)", True, _time(lambda: OF.add_rms_norm_(x32, xb, w, 1e-5, bf, 1.0), 10, flush=flush),
+        T * W * 12, 0)
+    add("add_rmsnorm (llama, prefill)", True, _time(lambda: OF.add_rmsnorm(xb, xb, w, 1e-5), 10, flush=flush), T * W * 8, 0)
+    # ---- window attention with rotation
+    ld = H * d + G * (d + dv)
+    proj = torch.randn(T, ld + lt.width, device=dev).to(bf)
+    left, right = proj[:, :ld], proj[:, ld:]
+    add("rotate_heads_ (prefill: q and k in place, fp32 angles)", False, _time(lambda: A.rotate_qk_(left, wa, pos=meta.pos), 10, flush=flush),
+        T * (H + G) * wa.rotary.dims * 4, 0)
+    qkv_l = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    cos, sin = OF.rope_tables(prompt_len + 64, d, 10000.0, dev)
+    add("apply_rope (llama, prefill: q and k, table look-up)", True,
+        _time(lambda: OF.apply_rope(qkv_l[:, :(H + G) * d], cos, sin, meta.pos, H + G, d), 10, flush=flush), T * (H + G) * d * 4, 0)
+    rows_c = wa.cache_rows(prompt_len + 64)
+    kc = torch.zeros(batch, G, rows_c, d, device=dev, dtype=bf)
+    vc = torch.zeros(batch, G, rows_c, dv, device=dev, dtype=bf)
+    add("value_norm_store (prefill: cache fill)", False,
+        _time(lambda: A.value_norm_store(left, wa, 1e-5, kc, vc, meta.tok_slot, meta.pos, meta.remain), 10, flush=flush), T * G * (d + 3 * dv) * 2, 0)
+    v_n = A.value_norm_store(left, wa, 1e-5, None, None, meta.tok_slot, meta.pos, meta.remain)
+    pairs = batch * sum(min(p + 1, win) for p in range(prompt_len))
+    add("sink_window_attention (prefill, tcgen05, window)", False,
+        _time(lambda: A.sink_window_attention(left, v_n, wa, None, None, meta.pos, cu, prompt_len), 3, warmup=1, flush=flush),
+        T * (H * (d + dv) + G * (d + dv)) * 2, 2.0 * pairs * H * (d + dv))
+    full_pairs = batch * prompt_len * (prompt_len + 1) // 2
+    add("varlen attention tcgen05 (llama, prefill, full causal)", True,
+        _time(lambda: A.varlen_attention_qkv(qkv_l, cu, prompt_len, H, G, d, None, True), 5, flush=flush), T * (2 * H + 2 * G) * d * 2,
+        4.0 * full_pairs * H * d)
+    keys = min(ctx + 1, win)
+    rows_d = wa.cache_rows(ctx + 64)
+    kc = torch.randn(batch, G, rows_d, d, device=dev).to(bf)
+    vc = torch.randn(batch, G, rows_d, dv, device=dev).to(bf)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    q1 = torch.randn(batch, ld, device=dev).to(bf)
+    add(f"sink_window_decode_attention (ctx {ctx}, {keys} keys)", False,
+        _time(lambda: A.sink_window_decode_attention(q1, wa, None, None, kc, vc, lens, None, 1e-5), 10, flush=flush),
+        batch * keys * G * (d + dv) * 2, 2.0 * batch * H * keys * (d + dv))
+    kl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    vl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    qkv1 = torch.randn(batch, (H + 2 * G) * d, device=dev).to(bf)
+    cos2, sin2 = OF.rope_tables(ctx + 64, d, 10000.0, dev)
+    add(f"decode_attention (llama, ctx {ctx}, all {ctx + 1} keys)", True,
+        _time(lambda: A.decode_attention(qkv1, kl, vl, lens, H, G, d, None, cos2, sin2), 10, flush=flush),
+        batch * (ctx + 1) * G * d * 2 * 2, 4.0 * batch * H * (ctx + 1) * d)
+    # ---- decayed linear attention next to the matrix-memory LSTM
+    nu = 2 * HR * d + HR * dv
+    S = torch.zeros(batch, HR, d, dv, device=dev)
+    for label, dc, src in (("retention: rotation + key factor", rt, torch.randn(T, rt.width, device=dev).mul(0.5).to(bf)),
+                           ("lightning: SiLU", lt, right)):
+        add(f"decay_prepare (prefill, {label})", False, _time(lambda: RC.decay_prepare(src, dc, pos=meta.pos), 10, flush=flush), T * nu * 6, 0)
+    u = RC.decay_prepare(right, lt, pos=meta.pos)
+    add("decay_scan (prefill, fp32 recurrence)", False, _time(lambda: RC.decay_scan(u, lt, cu, S, slots), 3, warmup=1, flush=flush),
+        T * nu * 4 + T * HR * dv * 4, T * HR * 4.0 * d * dv, simt_fp32=True)
+    ldm = 2 * HR * d + 2 * HR * dv + (2 * HR + 7) // 8 * 8
+    pm = (torch.randn(T, ldm, device=dev) * 0.5).to(bf)
+    gb = torch.zeros(2 * HR, device=dev, dtype=bf)
+    Sm = torch.zeros(batch, HR, d, dv + 1, device=dev)
+    Mm = torch.zeros(batch, HR, device=dev)
+    import dataclasses
+    ml = dataclasses.replace(ml, n_heads=HR)
+    add("mlstm_scan (defilorn, prefill, fp32 recurrence)", True, _time(lambda: RC.mlstm_scan(pm, gb, ml, cu, Sm, Mm, slots), 3, warmup=1, flush=flush),
+        T * (2 * HR * d + HR * dv) * 2 + T * HR * (dv + 2) * 4, T * HR * 6.0 * d * (dv + 1), simt_fp32=True)
+    o = RC.decay_scan(u, lt, cu, S, slots)
+    wo = torch.ones(HR * dv, device=dev, dtype=bf)
+    gate = right[:, nu:]
+    add("decay_out (prefill, full-width norm + weight + sigmoid gate)", False, _time(lambda: RC.decay_out(o, lt, wo, gate, 1e-5, bf), 10, flush=flush),
+        T * HR * dv * 8, 0)
+    add("decay_out (prefill, per-head norm + SiLU gate)", False, _time(lambda: RC.decay_out(o, rt, None, gate, 1e-5, bf), 10, flush=flush),
+        T * HR * dv * 8, 0)
+    om, mm = RC.mlstm_scan(pm, gb, ml, cu, Sm, Mm, slots)
+    add("mlstm_out (defilorn, prefill)", True, _time(lambda: RC.mlstm_out(om, mm, wo, pm[:, 2 * HR * d + HR * dv:], 1e-5, bf), 10, flush=flush),
+        T * HR * dv * 8, 0)
+    u1 = torch.randn(batch, nu, device=dev) * 0.1
+    add("decay_step (decode: state read + write)", False, _time(lambda: RC.decay_step(u1, lt, S, None), 10, flush=flush),
+        batch * HR * d * dv * 8, batch * HR * 4.0 * d * dv, simt_fp32=True)
+    p1 = (torch.randn(batch, ldm, device=dev) * 0.5).to(bf)
+    add("mlstm_step (defilorn, decode: state read + write)", True, _time(lambda: RC.mlstm_step(p1, gb, ml, Sm, Mm, None), 10, flush=flush),
+        batch * HR * d * (dv + 1) * 8, batch * HR * 6.0 * d * (dv + 1), simt_fp32=True)
+    # ---- routing
+    E, k = s["experts"], s["top"]
+    wr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf)
+    add("softmax_router (sigmoid scores, prefill)", False, _time(lambda: lib().softmax_router(xb, wr, None, None, k, False, True), 10, flush=flush),
+        T * W * 2, 2.0 * T * W * E)
+    add("softmax_router (defilorn: softmax scores, prefill)", True, _time(lambda: lib().softmax_router(xb, wr, None, None, k, False, False), 10, flush=flush),
+        T * W * 2, 2.0 * T * W * E)
+    xd = xb[:batch]
+    probs, idx, _ = lib().softmax_router(xd, wr, None, None, k, False, True)
+    row, _ = lib().moe_dispatch(idx, E, E)
+    add("moe_gather (decode, rows times their routing weight)", False, _time(lambda: lib().moe_gather(xd, row, k, probs), 10, flush=flush),
+        batch * k * W * 4, 0)
+    add("moe_gather (defilorn, decode, plain copy)", True, _time(lambda: lib().moe_gather(xd, row, k), 10, flush=flush), batch * k * W * 4, 0)
+    return rows
+
+
 def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
-    assert design in ("rapodra", "tizodra", "defilorn")
+    assert design in ("rapodra", "tizodra", "defilorn", "buvesun")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     peaks = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
@@ -475,11 +644,12 @@ def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
         if "hbm_gbs" in d and "bf16_tflops" in d:
             peaks = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
     results = [dict(bench="peaks", **peaks)]
-    table = {"rapodra": SIZES, "tizodra": TIZODRA_SIZES, "defilorn": DEFILORN_SIZES}[design]
+    table = {"rapodra": SIZES, "tizodra": TIZODRA_SIZES, "defilorn": DEFILORN_SIZES, "buvesun": BUVESUN_SIZES}[design]
     for name in sizes or list(table):
         s = table[name]
         results += model_numbers(name, s, n_layers, batch=32, prompt_len=1024, new_tokens=33, dev=dev, design=design)
-        kn = {"rapodra": kernel_numbers, "tizodra": tizodra_kernel_numbers, "defilorn": defilorn_kernel_numbers}[design]
+        kn = {"rapodra": kernel_numbers, "tizodra": tizodra_kernel_numbers, "defilorn": defilorn_kernel_numbers,
+              "buvesun": buvesun_kernel_numbers}[design]
         results += kn(name, s, batch=32, prompt_len=1024, ctx=2048, dev=dev, peaks=peaks)
     for r in results:
         print(json.dumps(r), flush=True)

@@ -39,7 +39,8 @@ NVCC_FLAGS = [
     "-Xptxas", "-v", "--use_fast_math",
 ]
 # kernels that must keep IEEE division / exact expf (optimizer, the fp32-exact mechanisms of heterogeneous stacks) opt out of fast-math
-NO_FAST_MATH = {"adam.cu", "seqmix.cu", "latent_attn.cu", "posenc.cu", "sinkattn.cu", "delta.cu", "mlstm.cu", "latent_rope.cu", "moe_route.cu"}
+NO_FAST_MATH = {"adam.cu", "seqmix.cu", "latent_attn.cu", "posenc.cu", "sinkattn.cu", "delta.cu", "mlstm.cu", "latent_rope.cu", "moe_route.cu",
+                "centred_norm.cu", "decay.cu"}
 
 
 def _cutlass_include() -> list[str]:

@@ -42,11 +42,18 @@ int rb_latent_rope_assemble(const void*, int64_t, const void*, int64_t, const vo
 int rb_latent_query_rope(const void*, int64_t, int, const int*, const int*, const float*, float, float, float*, int, int, int, int, int, cudaStream_t);
 int rb_sigmoid_gate(void*, int, const void*, int64_t, int, int64_t, int, cudaStream_t);
 int rb_softmax_router(const void*, int64_t, int, const void*, int, const void*, int, const void*, int, float*, int64_t*, float*, int64_t, int, int, int,
-                      int, cudaStream_t);
+                      int, int, cudaStream_t);
 int rb_moe_combine(const void*, int, const void*, int64_t, int, const int64_t*, const float*, const int64_t*, const void*, int, const float*, void*, int,
-                   int64_t, int, int, int, cudaStream_t);
+                   int64_t, int, int, int, int, cudaStream_t);
 int rb_moe_dispatch(const int64_t*, int64_t*, int*, int, int, int, cudaStream_t);
-int rb_moe_gather(const void*, int64_t, int, const int64_t*, void*, int64_t, int, int, cudaStream_t);
+int rb_moe_gather(const void*, int64_t, int, const int64_t*, const float*, void*, int64_t, int, int, cudaStream_t);
+int rb_centred_norm(void*, int, const void*, int64_t, const void*, int64_t, int, float, float, const void*, const void*, const void*, int, float, void*,
+                    int, int64_t, int, float, cudaStream_t);
+int rb_rotate_heads(void*, int64_t, int, const int*, const int*, const int*, const float*, int64_t, int, int, int, int, cudaStream_t);
+int rb_decay_prepare(const void*, int64_t, int, float*, const int*, const int*, const int*, const float*, int64_t, int, int, int, int, int, int, float,
+                     cudaStream_t);
+int rb_decay_scan(const float*, int64_t, const float*, float*, const int*, float*, const int*, int, int, int, int, int, cudaStream_t);
+int rb_decay_out(const float*, const void*, int, const void*, int64_t, int, void*, int, int64_t, int, int, float, int, int, cudaStream_t);
 int rb_qk_head_norm(void*, int64_t, int, const void*, const void*, int64_t, int, int, int, float, cudaStream_t);
 int rb_diff_combine(const void*, int, const float*, void*, int, int64_t, int, int, int, float, float, cudaStream_t);
 }
@@ -186,7 +193,7 @@ void diff_combine(const Tensor& a, const Tensor& lam, Tensor out, int64_t H, int
 }
 
 // x [T, K], w [R, K] -> (weights [T, k] fp32, outputs [T, k] int64, gate [T] fp32 or empty): see moe_route.cu
-std::vector<Tensor> softmax_router(const Tensor& x, const Tensor& w, const OptT& corr, const OptT& u, int64_t k, bool renorm) {
+std::vector<Tensor> softmax_router(const Tensor& x, const Tensor& w, const OptT& corr, const OptT& u, int64_t k, bool renorm, bool sigmoid) {
   CHECK_ROWS(x); CHECK_IN(w);
   const int64_t T = x.size(0), K = x.size(1), R = w.size(0);
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && w.size(1) == K && R <= 64 && k >= 1 && k <= 8 && k <= R, "softmax_router: shapes");
@@ -198,27 +205,31 @@ std::vector<Tensor> softmax_router(const Tensor& x, const Tensor& w, const OptT&
   TORCH_CHECK(rb_softmax_router(x.data_ptr(), x.stride(0), dt_code(x), w.data_ptr(), dt_code(w), corr.has_value() ? corr->data_ptr() : nullptr,
                                 corr.has_value() ? dt_code(*corr) : 0, u.has_value() ? u->data_ptr() : nullptr, u.has_value() ? dt_code(*u) : 0,
                                 probs.data_ptr<float>(), idx.data_ptr<int64_t>(), u.has_value() ? gate.data_ptr<float>() : nullptr, T, (int)K, (int)R,
-                                (int)k, renorm ? 1 : 0, cur_stream()) == 0);
+                                (int)k, renorm ? 1 : 0, sigmoid ? 1 : 0, cur_stream()) == 0);
   return {probs, idx, gate};
 }
 
-// out[t] = sum_j probs[t, j] * (idx[t, j] < E ? y[row[t, j]] : x[t]) + gate[t] * y_shared[t]
+// out[t] = sum_j probs[t, j] * (idx[t, j] < E ? y[row[t, j]] : x[t]) + gate[t] * y_shared[t]   (unit: probs read as 1; no gate: 1)
 void moe_combine(const Tensor& y, const Tensor& x, const Tensor& row, const Tensor& probs, const Tensor& idx, const OptT& ysh, const OptT& gate,
-                 Tensor out, int64_t E) {
+                 Tensor out, int64_t E, bool unit) {
   CHECK_IN(y); CHECK_ROWS(x); CHECK_IN(row); CHECK_IN(probs); CHECK_IN(idx); CHECK_IN(out);
   const int64_t T = x.size(0), H = x.size(1), k = probs.size(1);
   TORCH_CHECK(y.dim() == 2 && y.size(1) == H && out.size(0) == T && out.size(1) == H && probs.size(0) == T && idx.numel() == T * k && row.numel() == T * k);
   TORCH_CHECK(row.scalar_type() == at::kLong && idx.scalar_type() == at::kLong && probs.scalar_type() == at::kFloat && k <= 8);
-  TORCH_CHECK(ysh.has_value() == gate.has_value());
+  TORCH_CHECK(ysh.has_value() || !gate.has_value());
   if (ysh.has_value()) {
-    CHECK_IN((*ysh)); CHECK_IN((*gate));
-    TORCH_CHECK(ysh->size(0) == T && ysh->size(1) == H && gate->numel() == T && gate->scalar_type() == at::kFloat);
+    CHECK_IN((*ysh));
+    TORCH_CHECK(ysh->size(0) == T && ysh->size(1) == H);
+  }
+  if (gate.has_value()) {
+    CHECK_IN((*gate));
+    TORCH_CHECK(gate->numel() == T && gate->scalar_type() == at::kFloat);
   }
   c10::cuda::CUDAGuard g(x.device());
   TORCH_CHECK(rb_moe_combine(y.data_ptr(), dt_code(y), x.data_ptr(), x.stride(0), dt_code(x), row.data_ptr<int64_t>(), probs.data_ptr<float>(),
                              idx.data_ptr<int64_t>(), ysh.has_value() ? ysh->data_ptr() : nullptr, ysh.has_value() ? dt_code(*ysh) : 0,
                              gate.has_value() ? gate->data_ptr<float>() : nullptr, out.data_ptr(), dt_code(out), T, (int)H, (int)k, (int)E,
-                             cur_stream()) == 0);
+                             unit ? 1 : 0, cur_stream()) == 0);
 }
 
 // idx [T, k] int64 (router outputs, E real experts of R) -> (row [T k] int64: place of each assignment in the order sorted by expert,
@@ -233,15 +244,107 @@ std::vector<Tensor> moe_dispatch(const Tensor& idx, int64_t E, int64_t R) {
   return {row, offsets};
 }
 
-// x [T, H], row [T k] -> xs [T k, H] with xs[row[i]] = x[i / k]
-Tensor moe_gather(const Tensor& x, const Tensor& row, int64_t k) {
+// x [T, H], row [T k] -> xs [T k, H] with xs[row[i]] = x[i / k] (times scale[i], fp32 [T k], when given)
+Tensor moe_gather(const Tensor& x, const Tensor& row, int64_t k, const OptT& scale) {
   CHECK_ROWS(x); CHECK_IN(row);
   TORCH_CHECK(row.scalar_type() == at::kLong && row.numel() == x.size(0) * k);
+  if (scale.has_value()) { CHECK_IN((*scale)); TORCH_CHECK(scale->scalar_type() == at::kFloat && scale->numel() == row.numel()); }
   c10::cuda::CUDAGuard g(x.device());
   Tensor xs = at::empty({row.numel(), x.size(1)}, x.options());
-  TORCH_CHECK(rb_moe_gather(x.data_ptr(), x.stride(0), dt_code(x), row.data_ptr<int64_t>(), xs.data_ptr(), row.numel(), (int)x.size(1), (int)k,
-                            cur_stream()) == 0);
+  TORCH_CHECK(rb_moe_gather(x.data_ptr(), x.stride(0), dt_code(x), row.data_ptr<int64_t>(), scale.has_value() ? scale->data_ptr<float>() : nullptr,
+                            xs.data_ptr(), row.numel(), (int)x.size(1), (int)k, cur_stream()) == 0);
   return xs;
+}
+
+// "layer" stacks (centred_norm.cu): res += mult * scale * LN(a y + b y2) * w_post, out = LN(res or the branch) * w_next
+void centred_norm(const OptT& res, const Tensor& y, const OptT& y2, double a, double b, const OptT& w_post, const OptT& scale, double mult,
+                  const OptT& w_next, const OptT& out, double eps) {
+  CHECK_ROWS(y);
+  const int64_t T = y.size(0), W = y.size(1);
+  const Tensor* wv = w_post.has_value() ? &*w_post : (w_next.has_value() ? &*w_next : nullptr);
+  TORCH_CHECK(wv != nullptr && w_next.has_value() == out.has_value() && (res.has_value() || out.has_value()), "centred_norm: arguments");
+  for (const OptT* o : {&w_post, &scale, &w_next})
+    if (o->has_value()) { CHECK_IN((**o)); TORCH_CHECK((*o)->numel() == W && (*o)->scalar_type() == wv->scalar_type()); }
+  if (res.has_value()) { CHECK_IN((*res)); TORCH_CHECK(res->numel() == T * W && w_post.has_value()); }
+  if (y2.has_value()) { CHECK_ROWS((*y2)); TORCH_CHECK(y2->size(0) == T && y2->size(1) == W && y2->scalar_type() == y.scalar_type()); }
+  if (out.has_value()) { CHECK_IN((*out)); TORCH_CHECK(out->numel() == T * W); }
+  c10::cuda::CUDAGuard g(y.device());
+  TORCH_CHECK(rb_centred_norm(res.has_value() ? res->data_ptr() : nullptr, res.has_value() ? dt_code(*res) : 0, y.data_ptr(), y.stride(0),
+                              y2.has_value() ? y2->data_ptr() : nullptr, y2.has_value() ? y2->stride(0) : 0, dt_code(y), (float)a, (float)b,
+                              w_post.has_value() ? w_post->data_ptr() : nullptr, scale.has_value() ? scale->data_ptr() : nullptr,
+                              w_next.has_value() ? w_next->data_ptr() : nullptr, dt_code(*wv), (float)mult,
+                              out.has_value() ? out->data_ptr() : nullptr, out.has_value() ? dt_code(*out) : 0, T, (int)W, (float)eps,
+                              cur_stream()) == 0);
+}
+
+// in place: the n_h heads of size d at the start of every row of x turn by the row's position (decay.cu)
+void rotate_heads_(Tensor x, const OptT& pos, const OptT& lens, const OptT& slots, const Tensor& inv_freq, int64_t n_h, int64_t d, int64_t dims,
+                   bool interleaved) {
+  CHECK_ROWS(x); CHECK_IN(inv_freq);
+  const int64_t T = x.size(0);
+  TORCH_CHECK(x.size(1) >= n_h * d && inv_freq.scalar_type() == at::kFloat && inv_freq.numel() >= dims / 2 && (pos.has_value() || lens.has_value()));
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(rb_rotate_heads(x.data_ptr(), x.stride(0), dt_code(x), int_ptr(pos, T, "pos"), int_ptr(lens, 1, "lens"), int_ptr(slots, T, "slots"),
+                              inv_freq.data_ptr<float>(), T, (int)n_h, (int)d, (int)dims, interleaved ? 1 : 0, cur_stream()) == 0);
+}
+
+// proj [T, ld] = [q (H d) | k (H d) | v (H dv) | ..] -> u [T, 2 H d + H dv] fp32 (decay.cu)
+void decay_prepare(const Tensor& proj, Tensor u, const OptT& pos, const OptT& lens, const OptT& slots, const OptT& inv_freq, int64_t H, int64_t d,
+                   int64_t dv, int64_t dims, bool interleaved, bool silu, double k_scale) {
+  CHECK_ROWS(proj); CHECK_IN(u);
+  const int64_t T = proj.size(0), n = 2 * H * d + H * dv;
+  TORCH_CHECK(proj.size(1) >= n && u.scalar_type() == at::kFloat && u.numel() == T * n);
+  const float* fp = nullptr;
+  if (dims > 0) {
+    TORCH_CHECK(inv_freq.has_value() && (pos.has_value() || lens.has_value()));
+    CHECK_IN((*inv_freq));
+    TORCH_CHECK(inv_freq->scalar_type() == at::kFloat && inv_freq->numel() >= dims / 2);
+    fp = inv_freq->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard g(proj.device());
+  TORCH_CHECK(rb_decay_prepare(proj.data_ptr(), proj.stride(0), dt_code(proj), u.data_ptr<float>(), int_ptr(pos, T, "pos"), int_ptr(lens, 1, "lens"),
+                               int_ptr(slots, T, "slots"), fp, T, (int)H, (int)d, (int)dv, (int)dims, interleaved ? 1 : 0, silu ? 1 : 0,
+                               (float)k_scale, cur_stream()) == 0);
+}
+
+// u [T, 2 H d + H dv] fp32; cu absent: decode step (row b = sequence b); state [n_slots, H, d, dv] fp32 or absent.  o [T, H, dv] fp32.
+void decay_scan(const Tensor& u, const Tensor& decay, Tensor o, const OptT& cu, const OptT& state, const OptT& slots, int64_t H, int64_t d,
+                int64_t dv, bool load_state) {
+  CHECK_IN(u); CHECK_IN(decay); CHECK_IN(o);
+  const int64_t T = u.size(0);
+  TORCH_CHECK(u.scalar_type() == at::kFloat && u.dim() == 2 && u.size(1) == 2 * H * d + H * dv && decay.scalar_type() == at::kFloat &&
+              decay.numel() == H && o.scalar_type() == at::kFloat && o.numel() == T * H * dv);
+  int n_seqs = (int)T;
+  const int* cup = nullptr;
+  if (cu.has_value()) {
+    CHECK_IN((*cu));
+    TORCH_CHECK(cu->scalar_type() == at::kInt && cu->numel() >= 1);
+    cup = cu->data_ptr<int>();
+    n_seqs = (int)cu->numel() - 1;
+  }
+  float* sp = nullptr;
+  if (state.has_value()) {
+    CHECK_IN((*state));
+    TORCH_CHECK(state->scalar_type() == at::kFloat && state->dim() == 4 && state->size(1) == H && state->size(2) == d && state->size(3) == dv);
+    sp = state->data_ptr<float>();
+  }
+  TORCH_CHECK(sp != nullptr || !load_state, "decay_scan: load_state needs a state");
+  c10::cuda::CUDAGuard g(u.device());
+  TORCH_CHECK(rb_decay_scan(u.data_ptr<float>(), u.stride(0), decay.data_ptr<float>(), o.data_ptr<float>(), cup, sp, int_ptr(slots, n_seqs, "slots"),
+                            n_seqs, (int)H, (int)d, (int)dv, load_state ? 1 : 0, cur_stream()) == 0);
+}
+
+// o [T, H, dv] fp32 -> out [T, H dv]: per-head RMS norm, or one over all heads times w; times silu / sigmoid of gate [T, >= H dv]
+void decay_out(const Tensor& o, const OptT& w, const Tensor& gate, Tensor out, double eps, bool full, bool silu) {
+  CHECK_IN(o); CHECK_ROWS(gate); CHECK_IN(out);
+  TORCH_CHECK(o.dim() == 3 && o.scalar_type() == at::kFloat);
+  const int64_t T = o.size(0), H = o.size(1), dv = o.size(2);
+  TORCH_CHECK(gate.size(0) == T && gate.size(1) >= H * dv && out.numel() == T * H * dv && (!full || w.has_value()));
+  if (w.has_value()) { CHECK_IN((*w)); TORCH_CHECK(w->numel() == H * dv); }
+  c10::cuda::CUDAGuard g(o.device());
+  TORCH_CHECK(rb_decay_out(o.data_ptr<float>(), w.has_value() ? w->data_ptr() : nullptr, w.has_value() ? dt_code(*w) : 0, gate.data_ptr(),
+                           gate.stride(0), dt_code(gate), out.data_ptr(), dt_code(out), T, (int)H, (int)dv, (float)eps, full ? 1 : 0, silu ? 1 : 0,
+                           cur_stream()) == 0);
 }
 
 }  // namespace
@@ -254,9 +357,14 @@ void register_mix_ops(torch::Library& m) {
   m.def("latent_query_rope(Tensor q, Tensor lens, Tensor? slots, Tensor inv_freq, float mscale, float scale, Tensor(a!) qa, int d, int rot) -> ()", &latent_query_rope);
   m.def("sigmoid_gate_(Tensor(a!) x, Tensor gate) -> ()", &sigmoid_gate_);
   m.def("moe_dispatch(Tensor idx, int E, int R) -> Tensor[]", &moe_dispatch);
-  m.def("moe_gather(Tensor x, Tensor row, int k) -> Tensor", &moe_gather);
-  m.def("softmax_router(Tensor x, Tensor w, Tensor? corr, Tensor? u, int k, bool renorm) -> Tensor[]", &softmax_router);
-  m.def("moe_combine(Tensor y, Tensor x, Tensor row, Tensor probs, Tensor idx, Tensor? y_shared, Tensor? gate, Tensor(a!) out, int E) -> ()", &moe_combine);
+  m.def("moe_gather(Tensor x, Tensor row, int k, Tensor? scale=None) -> Tensor", &moe_gather);
+  m.def("softmax_router(Tensor x, Tensor w, Tensor? corr, Tensor? u, int k, bool renorm, bool sigmoid=False) -> Tensor[]", &softmax_router);
+  m.def("moe_combine(Tensor y, Tensor x, Tensor row, Tensor probs, Tensor idx, Tensor? y_shared, Tensor? gate, Tensor(a!) out, int E, bool unit=False) -> ()", &moe_combine);
+  m.def("centred_norm(Tensor(a!)? res, Tensor y, Tensor? y2, float a, float b, Tensor? w_post, Tensor? scale, float mult, Tensor? w_next, Tensor(b!)? out, float eps) -> ()", &centred_norm);
+  m.def("rotate_heads_(Tensor(a!) x, Tensor? pos, Tensor? lens, Tensor? slots, Tensor inv_freq, int n_h, int d, int dims, bool interleaved) -> ()", &rotate_heads_);
+  m.def("decay_prepare(Tensor proj, Tensor(a!) u, Tensor? pos, Tensor? lens, Tensor? slots, Tensor? inv_freq, int H, int d, int dv, int dims, bool interleaved, bool silu, float k_scale) -> ()", &decay_prepare);
+  m.def("decay_scan(Tensor u, Tensor decay, Tensor(a!) o, Tensor? cu, Tensor(b!)? state, Tensor? slots, int H, int d, int dv, bool load_state) -> ()", &decay_scan);
+  m.def("decay_out(Tensor o, Tensor? w, Tensor gate, Tensor(a!) out, float eps, bool full, bool silu) -> ()", &decay_out);
   m.def("qk_head_norm_(Tensor(a!) x, Tensor wq, Tensor wk, int nq, int nk, int d, float eps) -> ()", &qk_head_norm_);
   m.def("diff_combine(Tensor a, Tensor lam, Tensor(a!) out, int H, int G, int dv, float diff, float eps) -> ()", &diff_combine);
 }

@@ -1,0 +1,278 @@
+// Linear attention with a fixed decay per head (`DecayConfig`: retention, lightning attention) and the rotation of head vectors by
+// their position.  Per head a matrix state S [d, dv] in fp32:
+//
+//   S_t = g_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t                         (no softmax, no denominator)
+//
+// Everything is fp32 arithmetic with exact sinf / cosf / expf (compiled without fast-math); storage types by a type code.
+//
+//   rotate_heads   in place, a thread per pair: the first `dims` dimensions of each of the n_h heads at the start of a row turn by
+//                  angle = position * f_i (one fp32 product); pairs (i, i + dims / 2) or (2i, 2i + 1).  The position is pos[t], or in
+//                  the step form lens[slot of row t].
+//   decay_prepare  projection row [q (H d) | k (H d) | v (H dv) | ..] -> fp32 u [T, 2 H d + H dv]: SiLU on everything, or the rotation
+//                  of q and k and a factor on k.
+//   decay_scan     one CTA per (sequence, head, chunk of value columns).  A column of S depends only on its own value column, so a
+//                  group of LPC lanes owns one column with EPL rows per lane in registers.  The q, k and v of the next kTok tokens
+//                  arrive by cp.async into the second of two shared-memory buffers while the current ones are consumed (one
+//                  barrier per chunk); the lanes' partial dot products meet by shuffles.  The same kernel serves packed prompts
+//                  (state from zero or from the slot, left in the slot) and decode steps (sequences of one token).
+//   decay_out      one CTA per token: o / rms(o) per head, or over all heads times a weight; times silu or sigmoid of the gate.
+#include "anytype.cuh"
+
+namespace {
+
+using rb::ld_any;
+using rb::st_any;
+
+RB_DEVICE int row_position(const int* pos, const int* lens, const int* slots, int64_t t) {
+  if (pos != nullptr) return pos[t];
+  return lens[slots != nullptr ? slots[t] : t];
+}
+
+// ------------------------------------------------------------------------------------------------ rotation in place
+__global__ void __launch_bounds__(256) rotate_heads_kernel(void* __restrict__ x, int64_t ld, int dt, const int* __restrict__ pos,
+                                                           const int* __restrict__ lens, const int* __restrict__ slots,
+                                                           const float* __restrict__ inv_freq, int n_h, int d, int dims, int interleaved) {
+  const int64_t t = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const float p = (float)row_position(pos, lens, slots, t);
+  const int half = dims / 2;
+  for (int idx = threadIdx.x; idx < n_h * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half;
+    const int64_t e0 = t * ld + (int64_t)h * d + (interleaved ? 2 * i : i), e1 = e0 + (interleaved ? 1 : half);
+    float sn, cs;
+    sincosf(p * inv_freq[i], &sn, &cs);
+    const float u = ld_any(x, dt, e0), v = ld_any(x, dt, e1);
+    st_any(x, dt, e0, u * cs - v * sn);
+    st_any(x, dt, e1, v * cs + u * sn);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ prepare
+__global__ void __launch_bounds__(256) decay_prepare_kernel(const void* __restrict__ proj, int64_t ld, int dt, float* __restrict__ u,
+                                                            const int* __restrict__ pos, const int* __restrict__ lens,
+                                                            const int* __restrict__ slots, const float* __restrict__ inv_freq, int H, int d,
+                                                            int dv, int dims, int interleaved, int silu, float k_scale) {
+  const int64_t t = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const int nq = H * d, n = 2 * nq + H * dv, half = dims / 2;
+  const float p = dims > 0 ? (float)row_position(pos, lens, slots, t) : 0.f;
+  const int64_t base = t * ld;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float x = ld_any(proj, dt, base + c);
+    if (silu) x = x / (1.f + expf(-x));
+    if (c < 2 * nq) {
+      const int e = c % d;
+      if (e < dims) {
+        // partner of the pair and the sign of the sine term: (u, v) -> (u cos - v sin, v cos + u sin)
+        int i, partner;
+        bool first;
+        if (interleaved) { i = e >> 1; first = (e & 1) == 0; partner = first ? c + 1 : c - 1; }
+        else { first = e < half; i = first ? e : e - half; partner = first ? c + half : c - half; }
+        float y = ld_any(proj, dt, base + partner);
+        if (silu) y = y / (1.f + expf(-y));
+        float sn, cs;
+        sincosf(p * inv_freq[i], &sn, &cs);
+        x = first ? x * cs - y * sn : x * cs + y * sn;
+      }
+      if (c >= nq) x *= k_scale;
+    }
+    u[t * (int64_t)n + c] = x;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ scan
+constexpr int kThreads = 128;
+constexpr int scan_tokens(int dp) { return dp <= 128 ? 8 : (dp <= 512 ? 4 : 2); }
+
+struct ScanParams {
+  const float* u; int64_t ld;             // [T, ld] = [q (H d) | k (H d) | v (H dv)]
+  const float* decay;                     // [H]
+  float* o;                               // [T, H, dv]
+  const int* cu;                          // [n_seqs + 1]; null: sequence b is row b alone (decode step)
+  float* S;                               // [n_slots, H, d, dv] or null
+  const int* slots;                       // [n_seqs] or null (sequence b = slot b)
+  int H, d, dv, load_state;
+};
+
+RB_DEVICE void cp_async4(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
+}
+RB_DEVICE void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+RB_DEVICE void cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int LPC, int EPL>
+__global__ void __launch_bounds__(kThreads, EPL == 32 ? 3 : 2) decay_scan_kernel(ScanParams p) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int NCOL = kThreads / LPC, DP = LPC * EPL, kTok = scan_tokens(DP);
+  constexpr int kBuf = kTok * (2 * DP + NCOL);                     // floats of one staging buffer: q, k, v of kTok tokens
+  const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, c0 = blockIdx.z * NCOL;
+  const int l = tid % LPC, cl = tid / LPC;
+  const int d = p.d, dv = p.dv;
+  const int col = c0 + cl;
+  const bool active = col < dv;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const int t0 = p.cu ? p.cu[seq] : seq, t1 = p.cu ? p.cu[seq + 1] : seq + 1;
+  if (t1 <= t0) return;
+  const int64_t slot = p.slots ? p.slots[seq] : seq;
+  const float g = p.decay[h];
+  // lane l of a column owns rows ((e / 4) * LPC + l) * 4 + e % 4: float4 reads of k and q from shared memory without bank conflicts
+  auto row_of = [&](int e) { return ((e >> 2) * LPC + l) * 4 + (e & 3); };
+  float S[EPL];
+  float* Sg = p.S ? p.S + ((slot * p.H + h) * (int64_t)d) * dv : nullptr;
+  const bool load = p.load_state && Sg != nullptr;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int row = row_of(e);
+    S[e] = (load && active && row < d) ? Sg[(int64_t)row * dv + col] : 0.f;
+  }
+  // the padding rows d .. DP of the q / k staging rows are never written by cp.async: zero them once in both buffers
+  for (int idx = tid; idx < 2 * kBuf; idx += kThreads) smem[idx] = 0.f;
+  __syncthreads();
+  auto fetch = [&](float* buf, int tb) {
+    const int nt = min(kTok, t1 - tb);
+    for (int idx = tid; idx < nt * d; idx += kThreads) {
+      const int tt = idx / d, e = idx - tt * d;
+      const float* src = p.u + (int64_t)(tb + tt) * p.ld + h * d + e;
+      cp_async4(buf + tt * DP + e, src);
+      cp_async4(buf + kTok * DP + tt * DP + e, src + p.H * d);
+    }
+    for (int idx = tid; idx < nt * NCOL; idx += kThreads) {
+      const int tt = idx / NCOL, c = idx - tt * NCOL;
+      if (c0 + c < dv) cp_async4(buf + 2 * kTok * DP + tt * NCOL + c, p.u + (int64_t)(tb + tt) * p.ld + 2 * p.H * d + h * dv + c0 + c);
+    }
+    cp_commit();
+  };
+  fetch(smem, t0);
+  int which = 0;
+  for (int tb = t0; tb < t1; tb += kTok, which ^= 1) {
+    const int nt = min(kTok, t1 - tb);
+    float* buf = smem + which * kBuf;
+    cp_wait_all();
+    __syncthreads();                       // this chunk has landed for every thread; the other buffer is no longer read
+    if (tb + kTok < t1) fetch(smem + (which ^ 1) * kBuf, tb + kTok);
+    const float* qs = buf;
+    const float* ks = buf + kTok * DP;
+    const float* vs = ks + kTok * DP;
+#pragma unroll 1
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = vs[tt * NCOL + cl];
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DP) + l;
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DP) + l;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int e4 = 0; e4 < EPL / 4; ++e4) {
+        const float4 kk = k4[e4 * LPC], qq = q4[e4 * LPC];
+        S[e4 * 4] = fmaf(g, S[e4 * 4], kk.x * v);         a0 = fmaf(S[e4 * 4], qq.x, a0);
+        S[e4 * 4 + 1] = fmaf(g, S[e4 * 4 + 1], kk.y * v); a1 = fmaf(S[e4 * 4 + 1], qq.y, a1);
+        S[e4 * 4 + 2] = fmaf(g, S[e4 * 4 + 2], kk.z * v); a2 = fmaf(S[e4 * 4 + 2], qq.z, a2);
+        S[e4 * 4 + 3] = fmaf(g, S[e4 * 4 + 3], kk.w * v); a3 = fmaf(S[e4 * 4 + 3], qq.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+      for (int off = 1; off < LPC; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (l == 0 && active) p.o[((int64_t)(tb + tt) * p.H + h) * dv + col] = acc;
+    }
+  }
+  if (Sg != nullptr) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const int row = row_of(e);
+      if (active && row < d) Sg[(int64_t)row * dv + col] = S[e];
+    }
+  }
+}
+
+template <int LPC, int EPL>
+int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
+  constexpr int NCOL = kThreads / LPC, DP = LPC * EPL, kTok = scan_tokens(DP);
+  const size_t smem = sizeof(float) * 2 * (size_t)kTok * (2 * DP + NCOL);
+  auto kern = decay_scan_kernel<LPC, EPL>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+  dim3 grid((unsigned)n_seqs, (unsigned)p.H, (unsigned)RB_CEIL_DIV(p.dv, NCOL));
+  return rb::launch_pdl(kern, grid, dim3(kThreads), smem, s, p) == cudaSuccess ? 0 : 2;
+}
+
+// ------------------------------------------------------------------------------------------------ output norm and gate
+__global__ void __launch_bounds__(128) decay_out_kernel(const float* __restrict__ o, const void* __restrict__ w, int dtw, const void* __restrict__ gate,
+                                                        int64_t ldg, int dtg, void* __restrict__ out, int dto, int H, int dv, float eps, int full,
+                                                        int silu) {
+  __shared__ float red[32];
+  __shared__ float s_r;
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n = H * dv;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const float* orow = o + t * (int64_t)n;
+  auto emit = [&](int c, float r) {
+    const float gv = ld_any(gate, dtg, t * ldg + c);
+    const float sg = 1.f / (1.f + expf(-gv));
+    float y = orow[c] * r;
+    if (w != nullptr) y *= ld_any(w, dtw, c);
+    st_any(out, dto, t * (int64_t)n + c, y * (silu ? gv * sg : sg));
+  };
+  if (full) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) ss = fmaf(orow[c], orow[c], ss);
+    ss = rb::block_reduce<false>(ss, red);
+    if (threadIdx.x == 0) s_r = 1.f / sqrtf(ss / (float)n + eps);
+    __syncthreads();
+    const float r = s_r;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) emit(c, r);
+    return;
+  }
+  for (int h = warp; h < H; h += 4) {
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(orow[h * dv + c], orow[h * dv + c], ss);
+    ss = rb::warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)dv + eps);
+    for (int c = lane; c < dv; c += 32) emit(h * dv + c, r);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int rb_rotate_heads(void* x, int64_t ld, int dt, const int* pos, const int* lens, const int* slots, const float* inv_freq, int64_t T, int n_h, int d,
+                    int dims, int interleaved, cudaStream_t s) {
+  if (T == 0 || dims == 0) return 0;
+  if (dims % 2 || dims > d || (pos == nullptr && lens == nullptr)) return -1;
+  return rb::launch_pdl(rotate_heads_kernel, dim3((unsigned)T), dim3(256), 0, s, x, ld, dt, pos, lens, slots, inv_freq, n_h, d, dims,
+                        interleaved) == cudaSuccess ? 0 : 2;
+}
+
+int rb_decay_prepare(const void* proj, int64_t ld, int dt, float* u, const int* pos, const int* lens, const int* slots, const float* inv_freq,
+                     int64_t T, int H, int d, int dv, int dims, int interleaved, int silu, float k_scale, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (dims % 2 || dims > d || (dims > 0 && ((pos == nullptr && lens == nullptr) || inv_freq == nullptr))) return -1;
+  return rb::launch_pdl(decay_prepare_kernel, dim3((unsigned)T), dim3(256), 0, s, proj, ld, dt, u, pos, lens, slots, inv_freq, H, d, dv, dims,
+                        interleaved, silu, k_scale) == cudaSuccess ? 0 : 2;
+}
+
+// u [T, ld] fp32; o [T, H, dv] fp32; cu null = decode step over n_seqs rows; S the slots' states (null: keep none).  load_state:
+// start from the slot's state instead of zero.  Head sizes d up to 1024.
+int rb_decay_scan(const float* u, int64_t ld, const float* decay, float* o, const int* cu, float* S, const int* slots, int n_seqs, int H, int d,
+                  int dv, int load_state, cudaStream_t s) {
+  if (n_seqs == 0) return 0;
+  if (d < 1 || d > 1024 || dv < 1) return -1;
+  ScanParams p{u, ld, decay, o, cu, S, slots, H, d, dv, load_state};
+  if (d <= 32) return launch_scan<1, 32>(p, n_seqs, s);
+  if (d <= 64) return launch_scan<2, 32>(p, n_seqs, s);
+  if (d <= 128) return launch_scan<2, 64>(p, n_seqs, s);
+  if (d <= 256) return launch_scan<4, 64>(p, n_seqs, s);
+  if (d <= 512) return launch_scan<8, 64>(p, n_seqs, s);
+  return launch_scan<16, 64>(p, n_seqs, s);
+}
+
+int rb_decay_out(const float* o, const void* w, int dtw, const void* gate, int64_t ldg, int dtg, void* out, int dto, int64_t T, int H, int dv,
+                 float eps, int full, int silu, cudaStream_t s) {
+  if (T == 0) return 0;
+  return rb::launch_pdl(decay_out_kernel, dim3((unsigned)T), dim3(128), 0, s, o, w, dtw, gate, ldg, dtg, out, dto, H, dv, eps, full,
+                        silu) == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

@@ -1,14 +1,15 @@
 // Mixture-of-experts routing and combination for stacks that route by the softmax over all router outputs (fp32 arithmetic, any
 // storage type; compiled without fast-math):
 //   softmax_router   one CTA per token: logits z = W x (fp32 accumulation, the columns split over four warps), s = softmax(z) over
-//                    all R outputs, the k largest of s + correction in descending order, their weights s (optionally divided by
-//                    their sum); also, with an extra vector u, the token's gate sigmoid(u . x).  x is read once per 8 outputs
-//                    (from L1 after the first pass).
+//                    all R outputs (or, `sigmoid`, s = 1 / (1 + exp(-z)) of every output on its own), the k largest of s + correction
+//                    in descending order, their weights s (optionally divided by their sum); also, with an extra vector u, the
+//                    token's gate sigmoid(u . x).  x is read once per 8 outputs (from L1 after the first pass).
 //   moe_combine      one CTA per token: out[t] = sum_j p[t, j] * (e[t, j] < E ? y[row[t, j]] : x[t]) + g[t] * y_shared[t], summed in the
 //                    order written, in fp32; y holds the expert outputs of the assignments sorted by expert, row[t, j] the place of
-//                    assignment (t, j) in that order; outputs e >= E are identity experts.
+//                    assignment (t, j) in that order; outputs e >= E are identity experts.  `unit`: every p is 1 (the routing weight
+//                    went into the experts' inputs); without g the shared expert's output is added as it is.
 //   moe_dispatch     up to 1024 assignments: their places in the order sorted by expert and the experts' row offsets, one CTA.
-//   moe_gather       the token rows copied into that order.
+//   moe_gather       the token rows copied into that order, optionally times the assignment's routing weight (fp32 product).
 #include "anytype.cuh"
 
 namespace {
@@ -20,7 +21,7 @@ constexpr int kMaxOutputs = 64, kMaxTop = 8;
 __global__ void __launch_bounds__(128) softmax_router_kernel(const void* __restrict__ x, int64_t ldx, int dtx, const void* __restrict__ w, int dtw,
                                                              const void* __restrict__ corr, int dtc, const void* __restrict__ u, int dtu,
                                                              float* __restrict__ probs, int64_t* __restrict__ idx, float* __restrict__ gate,
-                                                             int64_t T, int K, int R, int k, int renorm) {
+                                                             int64_t T, int K, int R, int k, int renorm, int sigmoid) {
   __shared__ float s_part[4][kMaxOutputs + 1];
   __shared__ float s_z[kMaxOutputs];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(128) softmax_router_kernel(const void* __restr
   const float mx = rb::warp_max(fmaxf(z0, z1));
   const float e0v = lane < R ? expf(z0 - mx) : 0.f, e1v = lane + 32 < R ? expf(z1 - mx) : 0.f;
   const float den = rb::warp_sum(e0v + e1v);
-  const float s0 = e0v / den, s1 = e1v / den;
+  const float s0 = sigmoid ? 1.f / (1.f + expf(-z0)) : e0v / den, s1 = sigmoid ? 1.f / (1.f + expf(-z1)) : e1v / den;
   float c0 = lane < R ? s0 + (corr != nullptr ? ld_any(corr, dtc, lane) : 0.f) : -INFINITY;
   float c1 = lane + 32 < R ? s1 + (corr != nullptr ? ld_any(corr, dtc, lane + 32) : 0.f) : -INFINITY;
   float sel_p[kMaxTop];
@@ -109,17 +110,18 @@ __global__ void __launch_bounds__(128) softmax_router_kernel(const void* __restr
 __global__ void __launch_bounds__(256) moe_combine_kernel(const void* __restrict__ y, int dty, const void* __restrict__ x, int64_t ldx, int dtx,
                                                           const int64_t* __restrict__ row, const float* __restrict__ probs,
                                                           const int64_t* __restrict__ idx, const void* __restrict__ ysh, int dts,
-                                                          const float* __restrict__ gate, void* __restrict__ out, int dto, int H, int k, int E) {
+                                                          const float* __restrict__ gate, void* __restrict__ out, int dto, int H, int k, int E,
+                                                          int unit) {
   const int64_t t = blockIdx.x;
   rb::pdl_trigger();
   rb::pdl_wait();
   float p[kMaxTop];
   int64_t r[kMaxTop];
   for (int j = 0; j < k; ++j) {
-    p[j] = probs[t * k + j];
+    p[j] = unit ? 1.f : probs[t * k + j];
     r[j] = idx[t * k + j] < E ? row[t * k + j] : -1;
   }
-  const float g = gate != nullptr ? gate[t] : 0.f;
+  const float g = gate != nullptr ? gate[t] : 1.f;
   const bool vec = (H & 3) == 0 && (ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ysh == nullptr || (reinterpret_cast<uintptr_t>(ysh) & 15) == 0);
   if (vec) {
@@ -174,14 +176,19 @@ __global__ void __launch_bounds__(1024) moe_dispatch_kernel(const int64_t* __res
   if (i <= E) offsets[i] = s_start[i];
 }
 
-// xs[row[i]] = x[i / k]: the token rows laid out in the sorted order
+// xs[row[i]] = x[i / k] (* scale[i]): the token rows laid out in the sorted order
 __global__ void __launch_bounds__(128) moe_gather_kernel(const void* __restrict__ x, int64_t ldx, int dt, const int64_t* __restrict__ row,
-                                                         void* __restrict__ xs, int H, int k) {
+                                                         const float* __restrict__ scale, void* __restrict__ xs, int H, int k) {
   const int64_t i = blockIdx.x;
   rb::pdl_trigger();
   rb::pdl_wait();
   const int64_t src = (i / k) * ldx, dst = row[i] * (int64_t)H;
   const int es = rb::elt_size(dt);
+  if (scale != nullptr) {
+    const float sc = scale[i];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) rb::st_any(xs, dt, dst + c, ld_any(x, dt, src + c) * sc);
+    return;
+  }
   if (((H * es) & 15) == 0 && ((ldx * es) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0) {
     const uint4* a = reinterpret_cast<const uint4*>(static_cast<const char*>(x) + src * es);
     uint4* b = reinterpret_cast<uint4*>(static_cast<char*>(xs) + dst * es);
@@ -194,19 +201,20 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const void* __restrict_
 }  // namespace
 
 extern "C" int rb_softmax_router(const void* x, int64_t ldx, int dtx, const void* w, int dtw, const void* corr, int dtc, const void* u, int dtu,
-                                 float* probs, int64_t* idx, float* gate, int64_t T, int K, int R, int k, int renorm, cudaStream_t s) {
+                                 float* probs, int64_t* idx, float* gate, int64_t T, int K, int R, int k, int renorm, int sigmoid, cudaStream_t s) {
   if (T == 0) return 0;
   if (R < 1 || R > kMaxOutputs || k < 1 || k > kMaxTop || k > R) return -1;
   return rb::launch_pdl(softmax_router_kernel, dim3((unsigned)T), dim3(128), 0, s, x, ldx, dtx, w, dtw, corr, dtc, u, dtu,
-                        probs, idx, gate, T, K, R, k, renorm) == cudaSuccess ? 0 : 2;
+                        probs, idx, gate, T, K, R, k, renorm, sigmoid) == cudaSuccess ? 0 : 2;
 }
 
 extern "C" int rb_moe_combine(const void* y, int dty, const void* x, int64_t ldx, int dtx, const int64_t* row, const float* probs, const int64_t* idx,
-                              const void* ysh, int dts, const float* gate, void* out, int dto, int64_t T, int H, int k, int E, cudaStream_t s) {
+                              const void* ysh, int dts, const float* gate, void* out, int dto, int64_t T, int H, int k, int E, int unit,
+                              cudaStream_t s) {
   if (T == 0) return 0;
   if (k < 1 || k > kMaxTop) return -1;
   return rb::launch_pdl(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, s, y, dty, x, ldx, dtx, row, probs, idx, ysh, dts, gate, out, dto, H, k,
-                        E) == cudaSuccess ? 0 : 2;
+                        E, unit) == cudaSuccess ? 0 : 2;
 }
 
 extern "C" int rb_moe_dispatch(const int64_t* idx, int64_t* back, int* offsets, int N, int E, int R, cudaStream_t s) {
@@ -214,7 +222,8 @@ extern "C" int rb_moe_dispatch(const int64_t* idx, int64_t* back, int* offsets, 
   return rb::launch_pdl(moe_dispatch_kernel, dim3(1), dim3(1024), 0, s, idx, back, offsets, N, E, R) == cudaSuccess ? 0 : 2;
 }
 
-extern "C" int rb_moe_gather(const void* x, int64_t ldx, int dt, const int64_t* row, void* xs, int64_t N, int H, int k, cudaStream_t s) {
+extern "C" int rb_moe_gather(const void* x, int64_t ldx, int dt, const int64_t* row, const float* scale, void* xs, int64_t N, int H, int k,
+                             cudaStream_t s) {
   if (N == 0) return 0;
-  return rb::launch_pdl(moe_gather_kernel, dim3((unsigned)N), dim3(128), 0, s, x, ldx, dt, row, xs, H, k) == cudaSuccess ? 0 : 2;
+  return rb::launch_pdl(moe_gather_kernel, dim3((unsigned)N), dim3(128), 0, s, x, ldx, dt, row, scale, xs, H, k) == cudaSuccess ? 0 : 2;
 }

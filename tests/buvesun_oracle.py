@@ -150,7 +150,7 @@ def forward(cfg: dict, sd: Dict[str, torch.Tensor], tokens: List[int], seq: Opti
     eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     T = len(tokens)
     pos = torch.arange(seq.n, seq.n + T)
-    x = sd["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
+    x = sd["embed"][torch.tensor(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     x0 = x
     lp = cfg.get("loop")
     order = []
@@ -187,3 +187,59 @@ def forward(cfg: dict, sd: Dict[str, torch.Tensor], tokens: List[int], seq: Opti
             layers_out.append(x.clone())
     seq.n += T
     return layer_norm(x, sd["final.norm"], eps) @ sd["head"].T
+
+
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    W, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    if cfg.get("loop"):
+        out["loop.in"] = (W, 2 * W)
+    for i, lay in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lay["mixer"]
+        out.update({p + "norm1": (W,), p + "norm1b": (W,), p + "ls1": (W,)})
+        if lay["type"] == "retention":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * d, W), p + "mix.k": (H * d, W), p + "mix.v": (H * dv, W), p + "mix.g": (H * dv, W), p + "mix.o": (W, H * dv)})
+        else:
+            a, b = m["left"], m["right"]
+            H, G, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            out.update({p + "mix.left.q": (H * d, W), p + "mix.left.k": (G * d, W), p + "mix.left.v": (G * dv, W), p + "mix.left.o": (W, H * dv)})
+            H, d, dv = b["heads"], b["dim"], b["vdim"]
+            out.update({p + "mix.right.q": (H * d, W), p + "mix.right.k": (H * d, W), p + "mix.right.v": (H * dv, W), p + "mix.right.g": (H * dv, W),
+                        p + "mix.right.o": (W, H * dv), p + "mix.right.norm": (H * dv,)})
+        f = lay.get("mlp")
+        if f is not None:
+            out.update({p + "norm2": (W,), p + "norm2b": (W,), p + "ls2": (W,), p + "mlp.router": (f["router"]["experts"], W)})
+            F = f["expert"]["ff"]
+            for e in range(f["router"]["experts"]):
+                out.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+            if f.get("shared"):
+                Fs = f["shared"]["ff"]
+                out.update({p + "mlp.shared.gate": (Fs, W), p + "mlp.shared.up": (Fs, W), p + "mlp.shared.down": (W, Fs)})
+    return out
+
+
+def random_checkpoint(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
+    """Random weights, every value exactly representable in bfloat16 (so that both serving types read the same numbers)."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in tensor_shapes(cfg).items():
+        if len(shape) == 1:                                   # norm weights and layer scales: around 1, never near 0
+            t = 1.0 + 0.25 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g)
+        elif name.endswith("mlp.router"):
+            t = torch.randn(shape, generator=g) * (3.0 / math.sqrt(shape[-1]))
+        else:
+            t = torch.randn(shape, generator=g) * (1.3 / math.sqrt(shape[-1]))
+        sd[name] = t.bfloat16().float()
+    return sd
+
+
+def greedy(cfg: dict, sd: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(cfg, sd, seq)[-1].argmax())
+        out.append(nxt)
+        seq.append(nxt)
+    return out
