@@ -590,7 +590,7 @@ def buvesun_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx:
         add(f"decay_prepare (prefill, {label})", False, _time(lambda: RC.decay_prepare(src, dc, pos=meta.pos), 10, flush=flush), T * nu * 6, 0)
     u = RC.decay_prepare(right, lt, pos=meta.pos)
     add("decay_scan (prefill, fp32 recurrence)", False, _time(lambda: RC.decay_scan(u, lt, cu, S, slots), 3, warmup=1, flush=flush),
-        T * nu * 4 + T * HR * dv * 4, T * HR * 4.0 * d * dv, simt_fp32=True)
+        T * nu * 4 + T * HR * dv * 4, T * HR * 5.0 * d * dv, simt_fp32=True)
     ldm = 2 * HR * d + 2 * HR * dv + (2 * HR + 7) // 8 * 8
     pm = (torch.randn(T, ldm, device=dev) * 0.5).to(bf)
     gb = torch.zeros(2 * HR, device=dev, dtype=bf)
@@ -612,7 +612,7 @@ def buvesun_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx:
         T * HR * dv * 8, 0)
     u1 = torch.randn(batch, nu, device=dev) * 0.1
     add("decay_step (decode: state read + write)", False, _time(lambda: RC.decay_step(u1, lt, S, None), 10, flush=flush),
-        batch * HR * d * dv * 8, batch * HR * 4.0 * d * dv, simt_fp32=True)
+        batch * HR * d * dv * 8, batch * HR * 5.0 * d * dv, simt_fp32=True)
     p1 = (torch.randn(batch, ldm, device=dev) * 0.5).to(bf)
     add("mlstm_step (defilorn, decode: state read + write)", True, _time(lambda: RC.mlstm_step(p1, gb, ml, Sm, Mm, None), 10, flush=flush),
         batch * HR * d * (dv + 1) * 8, batch * HR * 6.0 * d * (dv + 1), simt_fp32=True)

@@ -272,17 +272,46 @@ def _parallel_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches
     return y_l, OF.linear(_decay_branch(model, i, d, right, s), p[f"{i}.attn.o2.weight"])
 
 
-def _finish_layer_block(model, i: int, b, x: torch.Tensor, y) -> None:
+@dataclasses.dataclass
+class PendingBranch:
+    """A branch output of a "layer" stack that is still owed to the stream: x += mult * scale * LN(a y + b y2) * w.  The kernel that
+    computes the next norm (the next block's, the final one) adds it on the way."""
+    y: torch.Tensor
+    w: torch.Tensor
+    scale: Optional[torch.Tensor]
+    y2: Optional[torch.Tensor] = None
+    a: float = 1.0
+    b: float = 1.0
+
+
+def _add_pending(model, x: torch.Tensor, pb: PendingBranch, next_w: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    c = model.config
+    return OF.residual_add_centred_norm_(x, pb.y, pb.w, c.layer_norm_epsilon, pb.scale, c.residual_mult, pb.y2, pb.a, pb.b, next_w, model.dtype)
+
+
+def _finish_layer_block(model, i: int, b, x: torch.Tensor, y, defer: bool = False) -> Optional[PendingBranch]:
     """"layer" stacks: x += mult * ls * LN_post(mixer output), then the feed-forward sublayer likewise.  `y` is the mixer's output,
-    or the pair of branch outputs of a `parallel` block (summed with `branch_scales` inside the norm kernel)."""
-    c, p = model.config, model.p
-    eps, mult = c.layer_norm_epsilon, c.residual_mult
+    or the pair of branch outputs of a `parallel` block (summed with `branch_scales` inside the norm kernel).  With `defer` the
+    block's last branch is returned instead of added."""
+    p = model.p
     y, y2 = y if isinstance(y, tuple) else (y, None)
     sa, sb = b.branch_scales if y2 is not None else (1.0, 1.0)
-    h = OF.residual_add_centred_norm_(x, y, p[f"{i}.attn.ln_post.weight"], eps, p.get(f"{i}.attn.ls.weight"), mult, y2, sa, sb,
-                                      p[f"{i}.mlp.ln.weight"] if b.mlp is not None else None, model.dtype)
+    pb = PendingBranch(y, p[f"{i}.attn.ln_post.weight"], p.get(f"{i}.attn.ls.weight"), y2, sa, sb)
     if b.mlp is not None:
-        OF.residual_add_centred_norm_(x, _mlp(model, i, h, b.mlp), p[f"{i}.mlp.ln_post.weight"], eps, p.get(f"{i}.mlp.ls.weight"), mult)
+        h = _add_pending(model, x, pb, p[f"{i}.mlp.ln.weight"])
+        pb = PendingBranch(_mlp(model, i, h, b.mlp), p[f"{i}.mlp.ln_post.weight"], p.get(f"{i}.mlp.ls.weight"))
+    if defer:
+        return pb
+    _add_pending(model, x, pb)
+    return None
+
+
+def _first_layer_norm(model, i: int, x: torch.Tensor, pending) -> torch.Tensor:
+    """Input of block i's mixer in a "layer" stack; a branch the previous block left pending is added by the same kernel."""
+    w = model.p[f"{i}.attn.ln.weight"]
+    if isinstance(pending, PendingBranch):
+        return _add_pending(model, x, pending, w)
+    return OF.centred_norm(settle(model, x, pending), w, model.config.layer_norm_epsilon, model.dtype)
 
 
 def norm_offset(c) -> float:
@@ -315,6 +344,9 @@ def first_norm(model, i: int, x: torch.Tensor, pending: Optional[torch.Tensor]) 
 
 def settle(model, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
     """Add a branch output that a block left pending (the caller needs the stream itself)."""
+    if isinstance(pending, PendingBranch):
+        _add_pending(model, x, pending)
+        return x
     if pending is not None:
         OF.residual_add_norm_(x, pending, None, 1, model.config.layer_norm_epsilon)
     return x
@@ -355,11 +387,10 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta, pend
     G, eps = c.norm_groups, c.layer_norm_epsilon
     keep = meta.k is not None
     if c.layer_norm_type == "layer":
-        h = OF.centred_norm(settle(model, x, pending), p[f"{i}.attn.ln.weight"], eps, model.dtype)
+        h = _first_layer_norm(model, i, x, pending)
         mixer = {"window_attention": _window_attention_packed, "delta": _delta_packed, "mlstm": _mlstm_packed, "latent_attention": _latent_rope_packed,
                  "decay": _decay_packed, "parallel": _parallel_packed}[b.mixer]
-        _finish_layer_block(model, i, b, x, mixer(model, i, li, h, meta))
-        return x, None
+        return x, _finish_layer_block(model, i, b, x, mixer(model, i, li, h, meta), defer)
     if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G, eps,
@@ -414,9 +445,8 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     if c.layer_norm_type == "layer":
-        h = OF.centred_norm(settle(model, x, pending), p[f"{i}.attn.ln.weight"], eps, model.dtype)
-        _finish_layer_block(model, i, b, x, _mixer_decode(model, b, i, li, h, k_caches, v_caches, m_caches, cache_lens, slots))
-        return x, None
+        h = _first_layer_norm(model, i, x, pending)
+        return x, _finish_layer_block(model, i, b, x, _mixer_decode(model, b, i, li, h, k_caches, v_caches, m_caches, cache_lens, slots), defer)
     if b.mixer != "latent_attention" or a.rotated:
         defer = defer and plain_prenorm(c)
         h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input_step(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G,
@@ -443,7 +473,9 @@ def final_norm(model, x: torch.Tensor, pending: Optional[torch.Tensor] = None) -
     c = model.config
     w = model.p[f"{c.n_layers}.ln_f.weight"]
     if c.layer_norm_type == "layer":
-        return OF.centred_norm(settle(model, x, pending), w, c.layer_norm_epsilon, model.dtype)
+        if isinstance(pending, PendingBranch):
+            return _add_pending(model, x, pending, w)
+        return OF.centred_norm(x, w, c.layer_norm_epsilon, model.dtype)
     if pending is not None and plain_prenorm(c):
         return OF.add_rms_norm_(x, pending, w, c.layer_norm_epsilon, model.dtype, norm_offset(c))
     return OF.sublayer_input(settle(model, x, pending), w, c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype, w_offset=norm_offset(c))

@@ -212,7 +212,12 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None, clamp: Optional[Tuple
     w_sorted = probs.reshape(-1)[order]
     if mcfg.scale_input:
         assert not ep and not n_id, "scale_input: local experts, no identity experts"
-        x_scaled = _scaled_rows(h, tok, w_sorted)
+        if fused:      # one kernel: every assignment's token row times its weight, written at its place in the sorted order
+            from realhf_b200.ops import lib
+            back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
+            x_scaled = lib().moe_gather(h, back, k, probs.float().contiguous())
+        else:
+            x_scaled = _scaled_rows(h, tok, w_sorted)
         w_sorted = torch.ones_like(w_sorted)
     if ep and sp:
         from realhf_b200.parallel import ep as EP
@@ -289,7 +294,8 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None, clamp: Optional[Tuple
         y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, act)
     if fused:
         from realhf_b200.ops import lib
-        back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
+        if not mcfg.scale_input:
+            back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
         out = torch.empty(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
         lib().moe_combine(y_sorted.contiguous(), h, back, probs.float().contiguous(), idx,
                           _shared_mlp(model, i, h, mcfg, act) if mcfg.shared_ff else None, gate_sh, out, E, bool(mcfg.scale_input))

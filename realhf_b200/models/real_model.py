@@ -369,7 +369,7 @@ class ReaLModel(nn.Module):
         if c.fp32_residual:
             x = x.float()
         if c.embed_scale is not None:
-            x = x * torch.tensor(c.embed_scale, dtype=x.dtype, device=x.device)
+            x = x * float(c.embed_scale)     # (a Python scalar: legal inside a CUDA-graph capture)
         return self._dropout(x, c.embd_pdrop)
 
     # ------------------------------------------------------------------ dropout under tensor parallelism

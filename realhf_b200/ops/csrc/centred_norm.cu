@@ -8,7 +8,10 @@
 //   out    = LN_next(res)            or, without res,   out = LN_next(branch)
 //
 // One CTA per row; every reduction runs over a fixed thread-to-element map and a fixed tree, so a row's result does not depend on
-// the batch it is in.  Rows of a multiple of 4 elements with 16-byte aligned tensors take 16-byte / 8-byte accesses.
+// the batch it is in.  Rows of a multiple of 4 elements (up to 8192) with 16-byte aligned tensors keep the row in registers, four
+// consecutive elements per 16-byte / 8-byte access: the residual row is fetched before the first reduction, and each norm takes two
+// block reductions over the registers (the sum, then the squared deviations from the mean).  Other rows go through shared memory,
+// element by element.
 #include "anytype.cuh"
 
 namespace {
@@ -94,6 +97,83 @@ __global__ void __launch_bounds__(kThreads) centred_norm_kernel(NormParams p) {
   }
 }
 
+// ---- register form
+// mean and reciprocal standard deviation of the row held as NV float4 per thread
+template <int NV>
+RB_DEVICE void reg_stats(const float4 (&v)[NV], int W, float eps, float* red, float& mean, float& rstd) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+    if ((threadIdx.x + j * kThreads) * 4 < W) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  mean = rb::block_reduce<false>(s, red) / (float)W;
+  float m2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+    if ((threadIdx.x + j * kThreads) * 4 < W) {
+      const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+      m2 += (a * a + b * b) + (c * c + d * d);
+    }
+  rstd = 1.f / sqrtf(rb::block_reduce<false>(m2, red) / (float)W + eps);
+}
+
+// NV float4 per thread: rows of up to NV * 1024 elements
+template <int NV>
+__global__ void __launch_bounds__(kThreads) centred_norm_reg_kernel(NormParams p) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const int W = p.W;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  float4 v[NV], r[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int e = (threadIdx.x + j * kThreads) * 4;
+    if (e < W) {
+      v[j] = rb::ld4_any(p.y, p.dty, t * p.ldy + e);
+      v[j] = make_float4(v[j].x * p.a, v[j].y * p.a, v[j].z * p.a, v[j].w * p.a);
+      if (p.y2 != nullptr) {
+        const float4 u = rb::ld4_any(p.y2, p.dty, t * p.ldy2 + e);
+        v[j] = make_float4(fmaf(u.x, p.b, v[j].x), fmaf(u.y, p.b, v[j].y), fmaf(u.z, p.b, v[j].z), fmaf(u.w, p.b, v[j].w));
+      }
+      if (p.res != nullptr) r[j] = rb::ld4_any(p.res, p.dtr, t * (int64_t)W + e);
+    }
+  }
+  if (p.res != nullptr) {
+    float mean, rstd;
+    reg_stats<NV>(v, W, p.eps, red, mean, rstd);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int e = (threadIdx.x + j * kThreads) * 4;
+      if (e < W) {
+        // the same products, in the same order, as the element-wise form: ((v - mean) rstd w_post) scale, times mult, plus res
+        const float4 wp = rb::ld4_any(p.w_post, p.dtw, e);
+        float4 n = make_float4((v[j].x - mean) * rstd * wp.x, (v[j].y - mean) * rstd * wp.y, (v[j].z - mean) * rstd * wp.z, (v[j].w - mean) * rstd * wp.w);
+        if (p.scale != nullptr) { const float4 g = rb::ld4_any(p.scale, p.dtw, e); n = make_float4(n.x * g.x, n.y * g.y, n.z * g.z, n.w * g.w); }
+        r[j] = make_float4(r[j].x + p.mult * n.x, r[j].y + p.mult * n.y, r[j].z + p.mult * n.z, r[j].w + p.mult * n.w);
+        rb::st4_any(p.res, p.dtr, t * (int64_t)W + e, r[j]);
+        v[j] = make_float4(rb::round_any(p.dtr, r[j].x), rb::round_any(p.dtr, r[j].y), rb::round_any(p.dtr, r[j].z), rb::round_any(p.dtr, r[j].w));
+      }
+    }
+    if (p.out == nullptr) return;
+  }
+  float mean, rstd;
+  reg_stats<NV>(v, W, p.eps, red, mean, rstd);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int e = (threadIdx.x + j * kThreads) * 4;
+    if (e < W) {
+      const float4 w = rb::ld4_any(p.w_next, p.dtw, e);
+      rb::st4_any(p.out, p.dto, t * (int64_t)W + e,
+                  make_float4((v[j].x - mean) * rstd * w.x, (v[j].y - mean) * rstd * w.y, (v[j].z - mean) * rstd * w.z, (v[j].w - mean) * rstd * w.w));
+    }
+  }
+}
+
+template <int NV>
+int launch_reg(const NormParams& p, int64_t T, cudaStream_t s) {
+  return rb::launch_pdl(centred_norm_reg_kernel<NV>, dim3((unsigned)T), dim3(kThreads), 0, s, p) == cudaSuccess ? 0 : 2;
+}
+
 inline bool al16(const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
 }  // namespace
@@ -108,6 +188,12 @@ extern "C" int rb_centred_norm(void* res, int dtr, const void* y, int64_t ldy, c
   if (smem > 160 * 1024) return -1;
   NormParams p{res, dtr, y, ldy, dty, y2, ldy2, a, b, w_post, scale, w_next, dtw, mult, out, dto, W, eps};
   const bool vec = W % 4 == 0 && ldy % 4 == 0 && (y2 == nullptr || ldy2 % 4 == 0) && al16(y) && al16(y2) && al16(w_next) && al16(out);
+  if (vec && W <= 8192 && al16(res) && al16(w_post) && al16(scale)) {
+    if (W <= 1024) return launch_reg<1>(p, T, s);
+    if (W <= 2048) return launch_reg<2>(p, T, s);
+    if (W <= 4096) return launch_reg<4>(p, T, s);
+    return launch_reg<8>(p, T, s);
+  }
   auto kern = vec ? centred_norm_kernel<true> : centred_norm_kernel<false>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
   return rb::launch_pdl(kern, dim3((unsigned)T), dim3(kThreads), smem, s, p) == cudaSuccess ? 0 : 2;

@@ -5,7 +5,7 @@
 //
 // Everything is fp32 arithmetic with exact sinf / cosf / expf (compiled without fast-math); storage types by a type code.
 //
-//   rotate_heads   in place, a thread per pair: the first `dims` dimensions of each of the n_h heads at the start of a row turn by
+//   rotate_heads   in place, a CTA per token (its cos / sin table formed once in shared memory): the first `dims` dimensions of each of the n_h heads at the start of a row turn by
 //                  angle = position * f_i (one fp32 product); pairs (i, i + dims / 2) or (2i, 2i + 1).  The position is pos[t], or in
 //                  the step form lens[slot of row t].
 //   decay_prepare  projection row [q (H d) | k (H d) | v (H dv) | ..] -> fp32 u [T, 2 H d + H dv]: SiLU on everything, or the rotation
@@ -48,7 +48,85 @@ __global__ void __launch_bounds__(256) rotate_heads_kernel(void* __restrict__ x,
   }
 }
 
+// One CTA per token: the token's cos / sin table (dims / 2 entries) is formed once in shared memory, then every thread turns four
+// consecutive elements per step (8- or 16-byte accesses): interleaved layout = two pairs inside the four; half layout = the four
+// elements at i .. i + 3 of the first half with their partners in the second half.
+constexpr int kMaxHalf = 512;
+
+RB_DEVICE void fill_table(float* cs, float* sn, float p, const float* inv_freq, int half) {
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &sn[i], &cs[i]);
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) rotate_heads_vec_kernel(void* __restrict__ x, int64_t ld, int dt, const int* __restrict__ pos,
+                                                               const int* __restrict__ lens, const int* __restrict__ slots,
+                                                               const float* __restrict__ inv_freq, int n_h, int d, int dims, int interleaved) {
+  __shared__ float cs[kMaxHalf], sn[kMaxHalf];
+  const int64_t t = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const int half = dims / 2, per_head = (interleaved ? dims : half) / 4;
+  fill_table(cs, sn, (float)row_position(pos, lens, slots, t), inv_freq, half);
+  for (int r = threadIdx.x; r < n_h * per_head; r += blockDim.x) {
+    const int h = r / per_head, c = (r - h * per_head) * 4;
+    const int64_t e0 = t * ld + (int64_t)h * d + c;
+    if (interleaved) {
+      const float4 v = rb::ld4_any(x, dt, e0);
+      const float c0 = cs[c / 2], s0 = sn[c / 2], c1 = cs[c / 2 + 1], s1 = sn[c / 2 + 1];
+      rb::st4_any(x, dt, e0, make_float4(v.x * c0 - v.y * s0, v.y * c0 + v.x * s0, v.z * c1 - v.w * s1, v.w * c1 + v.z * s1));
+    } else {
+      const float4 u = rb::ld4_any(x, dt, e0), v = rb::ld4_any(x, dt, e0 + half);
+      const float* k = cs + c;
+      const float* m = sn + c;
+      rb::st4_any(x, dt, e0, make_float4(u.x * k[0] - v.x * m[0], u.y * k[1] - v.y * m[1], u.z * k[2] - v.z * m[2], u.w * k[3] - v.w * m[3]));
+      rb::st4_any(x, dt, e0 + half, make_float4(v.x * k[0] + u.x * m[0], v.y * k[1] + u.y * m[1], v.z * k[2] + u.z * m[2], v.w * k[3] + u.w * m[3]));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ prepare
+RB_DEVICE float silu1(float x) { return x / (1.f + expf(-x)); }
+RB_DEVICE float4 silu4(float4 v) { return make_float4(silu1(v.x), silu1(v.y), silu1(v.z), silu1(v.w)); }
+
+// One CTA per token, four consecutive columns per thread and step, the cos / sin table in shared memory; a rotated group of four in
+// the half layout also reads its partner group.
+__global__ void __launch_bounds__(256) decay_prepare_vec_kernel(const void* __restrict__ proj, int64_t ld, int dt, float* __restrict__ u,
+                                                                const int* __restrict__ pos, const int* __restrict__ lens,
+                                                                const int* __restrict__ slots, const float* __restrict__ inv_freq, int H, int d,
+                                                                int dv, int dims, int interleaved, int silu, float k_scale) {
+  __shared__ float cs[kMaxHalf], sn[kMaxHalf];
+  const int64_t t = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  const int nq = H * d, n = 2 * nq + H * dv, half = dims / 2;
+  if (dims > 0) fill_table(cs, sn, (float)row_position(pos, lens, slots, t), inv_freq, half);
+  const int64_t base = t * ld;
+  for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+    float4 x = rb::ld4_any(proj, dt, base + c);
+    if (silu) x = silu4(x);
+    if (c < 2 * nq) {
+      const int e = c % d;
+      if (e < dims) {
+        if (interleaved) {
+          const float c0 = cs[e / 2], s0 = sn[e / 2], c1 = cs[e / 2 + 1], s1 = sn[e / 2 + 1];
+          x = make_float4(x.x * c0 - x.y * s0, x.y * c0 + x.x * s0, x.z * c1 - x.w * s1, x.w * c1 + x.z * s1);
+        } else {
+          const bool first = e < half;
+          const int i = first ? e : e - half;
+          float4 y = rb::ld4_any(proj, dt, base + (first ? c + half : c - half));
+          if (silu) y = silu4(y);
+          const float* k = cs + i;
+          const float* m = sn + i;
+          x = first ? make_float4(x.x * k[0] - y.x * m[0], x.y * k[1] - y.y * m[1], x.z * k[2] - y.z * m[2], x.w * k[3] - y.w * m[3])
+                    : make_float4(x.x * k[0] + y.x * m[0], x.y * k[1] + y.y * m[1], x.z * k[2] + y.z * m[2], x.w * k[3] + y.w * m[3]);
+        }
+      }
+      if (c >= nq) x = make_float4(x.x * k_scale, x.y * k_scale, x.z * k_scale, x.w * k_scale);
+    }
+    *reinterpret_cast<float4*>(u + t * (int64_t)n + c) = x;
+  }
+}
+
 __global__ void __launch_bounds__(256) decay_prepare_kernel(const void* __restrict__ proj, int64_t ld, int dt, float* __restrict__ u,
                                                             const int* __restrict__ pos, const int* __restrict__ lens,
                                                             const int* __restrict__ slots, const float* __restrict__ inv_freq, int H, int d,
@@ -94,11 +172,16 @@ struct ScanParams {
   float* S;                               // [n_slots, H, d, dv] or null
   const int* slots;                       // [n_seqs] or null (sequence b = slot b)
   int H, d, dv, load_state;
+  int vec;                                // rows allow 16-byte copies (d, dv, ld multiples of 4, u 16-byte aligned)
 };
 
 RB_DEVICE void cp_async4(float* dst, const float* src) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
+}
+RB_DEVICE void cp_async16(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(src) : "memory");
 }
 RB_DEVICE void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 RB_DEVICE void cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
@@ -134,6 +217,21 @@ __global__ void __launch_bounds__(kThreads, EPL == 32 ? 3 : 2) decay_scan_kernel
   __syncthreads();
   auto fetch = [&](float* buf, int tb) {
     const int nt = min(kTok, t1 - tb);
+    if (p.vec) {
+      const int d4 = d >> 2;
+      for (int idx = tid; idx < nt * d4; idx += kThreads) {
+        const int tt = idx / d4, e = (idx - tt * d4) * 4;
+        const float* src = p.u + (int64_t)(tb + tt) * p.ld + h * d + e;
+        cp_async16(buf + tt * DP + e, src);
+        cp_async16(buf + kTok * DP + tt * DP + e, src + p.H * d);
+      }
+      for (int idx = tid; idx < nt * (NCOL / 4); idx += kThreads) {
+        const int tt = idx / (NCOL / 4), c = (idx - tt * (NCOL / 4)) * 4;
+        if (c0 + c < dv) cp_async16(buf + 2 * kTok * DP + tt * NCOL + c, p.u + (int64_t)(tb + tt) * p.ld + 2 * p.H * d + h * dv + c0 + c);
+      }
+      cp_commit();
+      return;
+    }
     for (int idx = tid; idx < nt * d; idx += kThreads) {
       const int tt = idx / d, e = idx - tt * d;
       const float* src = p.u + (int64_t)(tb + tt) * p.ld + h * d + e;
@@ -241,6 +339,10 @@ int rb_rotate_heads(void* x, int64_t ld, int dt, const int* pos, const int* lens
                     int dims, int interleaved, cudaStream_t s) {
   if (T == 0 || dims == 0) return 0;
   if (dims % 2 || dims > d || (pos == nullptr && lens == nullptr)) return -1;
+  const int grp = (interleaved ? dims : dims / 2);
+  if (d % 4 == 0 && grp % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && dims / 2 <= kMaxHalf)
+    return rb::launch_pdl(rotate_heads_vec_kernel, dim3((unsigned)T), dim3(256), 0, s, x, ld, dt, pos, lens, slots, inv_freq, n_h, d, dims,
+                          interleaved) == cudaSuccess ? 0 : 2;
   return rb::launch_pdl(rotate_heads_kernel, dim3((unsigned)T), dim3(256), 0, s, x, ld, dt, pos, lens, slots, inv_freq, n_h, d, dims,
                         interleaved) == cudaSuccess ? 0 : 2;
 }
@@ -249,6 +351,11 @@ int rb_decay_prepare(const void* proj, int64_t ld, int dt, float* u, const int* 
                      int64_t T, int H, int d, int dv, int dims, int interleaved, int silu, float k_scale, cudaStream_t s) {
   if (T == 0) return 0;
   if (dims % 2 || dims > d || (dims > 0 && ((pos == nullptr && lens == nullptr) || inv_freq == nullptr))) return -1;
+  const int grp = (interleaved ? dims : dims / 2);
+  if (d % 4 == 0 && dv % 4 == 0 && grp % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(u) & 15) == 0 && dims / 2 <= kMaxHalf)
+    return rb::launch_pdl(decay_prepare_vec_kernel, dim3((unsigned)T), dim3(256), 0, s, proj, ld, dt, u, pos, lens, slots, inv_freq, H, d, dv, dims,
+                          interleaved, silu, k_scale) == cudaSuccess ? 0 : 2;
   return rb::launch_pdl(decay_prepare_kernel, dim3((unsigned)T), dim3(256), 0, s, proj, ld, dt, u, pos, lens, slots, inv_freq, H, d, dv, dims,
                         interleaved, silu, k_scale) == cudaSuccess ? 0 : 2;
 }
@@ -259,10 +366,11 @@ int rb_decay_scan(const float* u, int64_t ld, const float* decay, float* o, cons
                   int dv, int load_state, cudaStream_t s) {
   if (n_seqs == 0) return 0;
   if (d < 1 || d > 1024 || dv < 1) return -1;
-  ScanParams p{u, ld, decay, o, cu, S, slots, H, d, dv, load_state};
+  const int vec = d % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0;
+  ScanParams p{u, ld, decay, o, cu, S, slots, H, d, dv, load_state, vec};
   if (d <= 32) return launch_scan<1, 32>(p, n_seqs, s);
   if (d <= 64) return launch_scan<2, 32>(p, n_seqs, s);
-  if (d <= 128) return launch_scan<2, 64>(p, n_seqs, s);
+  if (d <= 128) return launch_scan<2, 64>(p, n_seqs, s);   // (4 lanes x 32 rows per column measured 20 % slower at d = 128)
   if (d <= 256) return launch_scan<4, 64>(p, n_seqs, s);
   if (d <= 512) return launch_scan<8, 64>(p, n_seqs, s);
   return launch_scan<16, 64>(p, n_seqs, s);

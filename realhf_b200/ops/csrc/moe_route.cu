@@ -186,6 +186,13 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const void* __restrict_
   const int es = rb::elt_size(dt);
   if (scale != nullptr) {
     const float sc = scale[i];
+    if ((H & 3) == 0 && (ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0) {
+      for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        const float4 v = rb::ld4_any(x, dt, src + c);
+        rb::st4_any(xs, dt, dst + c, make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc));
+      }
+      return;
+    }
     for (int c = threadIdx.x; c < H; c += blockDim.x) rb::st_any(xs, dt, dst + c, ld_any(x, dt, src + c) * sc);
     return;
   }
