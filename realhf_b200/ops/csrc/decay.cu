@@ -386,7 +386,7 @@ int rb_decay_scan(const float* u, int64_t ld, const float* decay, float* o, cons
   // thread halve the shared-memory reads of q and k per multiply-add (d = 128: 1.93 -> 1.60 ms for 32 x 1024 tokens x 16 heads)
   if (d <= 32) return launch_scan<1, 32, 1>(p, n_seqs, s);
   if (d <= 64) return launch_scan<2, 32, 2>(p, n_seqs, s);
-  if (d <= 128) return launch_scan<4, 32, 2>(p, n_seqs, s);
+  if (d <= 128) return launch_scan<4, 32, 2>(p, n_seqs, s);   // (four columns x 16 rows per lane: no faster, 1.64 ms)
   if (d <= 256) return launch_scan<8, 32, 2>(p, n_seqs, s);
   if (d <= 512) return launch_scan<16, 32, 2>(p, n_seqs, s);
   return launch_scan<32, 32, 2>(p, n_seqs, s);
