@@ -309,6 +309,7 @@ int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
 }
 
 // ------------------------------------------------------------------------------------------------ output norm and gate
+template <bool kVec>
 __global__ void __launch_bounds__(128) decay_out_kernel(const float* __restrict__ o, const void* __restrict__ w, int dtw, const void* __restrict__ gate,
                                                         int64_t ldg, int dtg, void* __restrict__ out, int dto, int H, int dv, float eps, int full,
                                                         int silu) {
@@ -319,29 +320,47 @@ __global__ void __launch_bounds__(128) decay_out_kernel(const float* __restrict_
   rb::pdl_trigger();
   rb::pdl_wait();
   const float* orow = o + t * (int64_t)n;
-  auto emit = [&](int c, float r) {
-    const float gv = ld_any(gate, dtg, t * ldg + c);
+  auto act = [&](float gv) {
     const float sg = 1.f / (1.f + expf(-gv));
-    float y = orow[c] * r;
-    if (w != nullptr) y *= ld_any(w, dtw, c);
-    st_any(out, dto, t * (int64_t)n + c, y * (silu ? gv * sg : sg));
+    return silu ? gv * sg : sg;
   };
+  auto emit = [&](int c, float r) {               // kVec: the four elements c .. c + 3
+    if constexpr (kVec) {
+      const float4 ov = *reinterpret_cast<const float4*>(orow + c), gv = rb::ld4_any(gate, dtg, t * ldg + c);
+      float4 y = make_float4(ov.x * r, ov.y * r, ov.z * r, ov.w * r);
+      if (w != nullptr) { const float4 wv = rb::ld4_any(w, dtw, c); y = make_float4(y.x * wv.x, y.y * wv.y, y.z * wv.z, y.w * wv.w); }
+      rb::st4_any(out, dto, t * (int64_t)n + c, make_float4(y.x * act(gv.x), y.y * act(gv.y), y.z * act(gv.z), y.w * act(gv.w)));
+    } else {
+      float y = orow[c] * r;
+      if (w != nullptr) y *= ld_any(w, dtw, c);
+      st_any(out, dto, t * (int64_t)n + c, y * act(ld_any(gate, dtg, t * ldg + c)));
+    }
+  };
+  auto sumsq = [&](int c) {
+    if constexpr (kVec) {
+      const float4 v = *reinterpret_cast<const float4*>(orow + c);
+      return (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    } else {
+      return orow[c] * orow[c];
+    }
+  };
+  constexpr int V = kVec ? 4 : 1;
   if (full) {
     float ss = 0.f;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) ss = fmaf(orow[c], orow[c], ss);
+    for (int c = threadIdx.x * V; c < n; c += blockDim.x * V) ss += sumsq(c);
     ss = rb::block_reduce<false>(ss, red);
     if (threadIdx.x == 0) s_r = 1.f / sqrtf(ss / (float)n + eps);
     __syncthreads();
     const float r = s_r;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) emit(c, r);
+    for (int c = threadIdx.x * V; c < n; c += blockDim.x * V) emit(c, r);
     return;
   }
   for (int h = warp; h < H; h += 4) {
     float ss = 0.f;
-    for (int c = lane; c < dv; c += 32) ss = fmaf(orow[h * dv + c], orow[h * dv + c], ss);
+    for (int c = lane * V; c < dv; c += 32 * V) ss += sumsq(h * dv + c);
     ss = rb::warp_sum(ss);
     const float r = 1.f / sqrtf(ss / (float)dv + eps);
-    for (int c = lane; c < dv; c += 32) emit(h * dv + c, r);
+    for (int c = lane * V; c < dv; c += 32 * V) emit(h * dv + c, r);
   }
 }
 
@@ -395,8 +414,10 @@ int rb_decay_scan(const float* u, int64_t ld, const float* decay, float* o, cons
 int rb_decay_out(const float* o, const void* w, int dtw, const void* gate, int64_t ldg, int dtg, void* out, int dto, int64_t T, int H, int dv,
                  float eps, int full, int silu, cudaStream_t s) {
   if (T == 0) return 0;
-  return rb::launch_pdl(decay_out_kernel, dim3((unsigned)T), dim3(128), 0, s, o, w, dtw, gate, ldg, dtg, out, dto, H, dv, eps, full,
-                        silu) == cudaSuccess ? 0 : 2;
+  auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = dv % 4 == 0 && ldg % 4 == 0 && al(o) && al(w) && al(gate) && al(out);
+  return rb::launch_pdl(vec ? decay_out_kernel<true> : decay_out_kernel<false>, dim3((unsigned)T), dim3(128), 0, s, o, w, dtw, gate, ldg, dtg, out,
+                        dto, H, dv, eps, full, silu) == cudaSuccess ? 0 : 2;
 }
 
 }  // extern "C"

@@ -1,4 +1,6 @@
-"""Recurrent mixers: the gated delta rule (`DeltaRuleConfig`) in packed (prefill) and one-token (decode) form.
+"""Recurrent mixers in packed (prefill) and one-token (decode) form: the gated delta rule (`DeltaRuleConfig`, below), the
+matrix-memory LSTM (`MLSTMConfig`) and linear attention with a fixed decay per head (`DecayConfig`), each introduced by a comment
+block further down.
 
 Per head, with a matrix state S [d, dv] in fp32:   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 (the output is read after the update, so it contains what this token just wrote).  Everything that enters the recurrence is fp32.
